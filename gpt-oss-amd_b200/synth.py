@@ -1,0 +1,107 @@
+"""Seeded synthetic inputs for the MoE block.
+
+Real gpt-oss checkpoints and prompts are not available offline, so every
+measurement and parity case uses tensors with the shapes and value
+distributions of the benchmark configurations:
+
+* activations  ``randn(T, H)`` rounded to bf16,
+* router       ``W = 0.02 * randn(E, H)`` rounded to bf16, ``b = 0.1 * randn(E)`` fp32,
+* experts      MXFP4: every block byte uniform in [0, 256) (two uniform e2m1
+  codes), scale byte ``127 + e`` with ``e`` uniform in {-8..-4}; fp32 biases
+  ``0.01 * randn``.
+
+Layouts follow the checkpoint format the reference exporter reads
+(tools/model_export/gpt-oss-20b/export_model_bin.py:95-133): ``blocks``
+``[E, rows, in/32, 16]`` uint8 and ``scales`` ``[E, rows, in/32]`` uint8, with
+``mlp1`` rows gate/up interleaved (src/run.cpp:667-670).
+
+Everything is generated with a CPU ``torch.Generator`` so the same seed gives
+the same bytes on every machine.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import numpy as np
+import torch
+
+
+@dataclasses.dataclass
+class MoEShape:
+    hidden: int = 2880
+    intermediate: int = 2880
+    n_experts: int = 32
+    top_k: int = 4
+    alpha: float = 1.702
+    limit: float = 7.0
+
+
+@dataclasses.dataclass
+class LayerWeights:
+    shape: MoEShape
+    w_router: np.ndarray  # [E, H] uint16 (bf16 bits)
+    b_router: np.ndarray  # [E] float32
+    blocks1: np.ndarray  # [E, 2I, H/32, 16] uint8
+    scales1: np.ndarray  # [E, 2I, H/32] uint8
+    bias1: np.ndarray  # [E, 2I] float32
+    blocks2: np.ndarray  # [E, H, I/32, 16] uint8
+    scales2: np.ndarray  # [E, H, I/32] uint8
+    bias2: np.ndarray  # [E, H] float32
+
+
+def bf16_bits(x: torch.Tensor) -> np.ndarray:
+    """float tensor -> uint16 array of its bf16 (RNE) bit patterns."""
+    return x.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def make_layer(shape: MoEShape, seed: int = 0, scale_lo: int = -8, scale_hi: int = -4,
+               zipf_s: float | None = None, zipf_gain: float = 1.0) -> LayerWeights:
+    """One layer's router + experts.  ``zipf_s`` replaces the router bias by
+    ``zipf_gain * log(pmf)`` of a Zipf(s) law over a seeded permutation of the
+    experts (the skewed-load configuration)."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    H, I, E = shape.hidden, shape.intermediate, shape.n_experts
+    w_router = bf16_bits(0.02 * torch.randn(E, H, generator=g))
+    b_router = (0.1 * torch.randn(E, generator=g)).numpy().astype(np.float32)
+    blocks1 = torch.randint(0, 256, (E, 2 * I, H // 32, 16), generator=g, dtype=torch.uint8).numpy()
+    scales1 = (127 + torch.randint(scale_lo, scale_hi + 1, (E, 2 * I, H // 32), generator=g)).to(
+        torch.uint8).numpy()
+    bias1 = (0.01 * torch.randn(E, 2 * I, generator=g)).numpy().astype(np.float32)
+    blocks2 = torch.randint(0, 256, (E, H, I // 32, 16), generator=g, dtype=torch.uint8).numpy()
+    scales2 = (127 + torch.randint(scale_lo, scale_hi + 1, (E, H, I // 32), generator=g)).to(
+        torch.uint8).numpy()
+    bias2 = (0.01 * torch.randn(E, H, generator=g)).numpy().astype(np.float32)
+    if zipf_s is not None:
+        perm = torch.randperm(E, generator=g).numpy()
+        pmf = 1.0 / np.arange(1, E + 1, dtype=np.float64) ** zipf_s
+        pmf /= pmf.sum()
+        b = np.empty(E, dtype=np.float64)
+        b[perm] = zipf_gain * np.log(pmf)
+        b_router = (b - b.mean()).astype(np.float32)
+    return LayerWeights(shape, w_router, b_router, blocks1, scales1, bias1, blocks2, scales2, bias2)
+
+
+def make_tokens(n_tokens: int, hidden: int, seed: int = 0) -> np.ndarray:
+    """[T, H] activations ~N(0,1) as bf16 bit patterns (uint16)."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(1_000_003 + seed)
+    return bf16_bits(torch.randn(n_tokens, hidden, generator=g))
+
+
+#: flops and bytes of one call, as used for the roofline figures
+def moe_flops(n_tokens: int, shape: MoEShape) -> float:
+    H, I, E, K = shape.hidden, shape.intermediate, shape.n_experts, shape.top_k
+    return float(n_tokens) * (2.0 * K * (2 * I * H + H * I) + 2.0 * E * H)
+
+
+def moe_decode_bytes(n_tokens: int, shape: MoEShape, active_experts: int | None = None) -> float:
+    H, I, E = shape.hidden, shape.intermediate, shape.n_experts
+    ea = E if active_experts is None else active_experts
+    per_expert = (2 * I * H + H * I) // 2 + (2 * I * H + H * I) // 32 + (2 * I + H) * 4
+    return float(ea * per_expert + E * H * 2 + E * 4 + n_tokens * H * 2 + n_tokens * H * 4)
