@@ -1,0 +1,141 @@
+// Shared definitions of the MoE kernels: resident weight layout, MXFP4 decode,
+// status codes.  sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace moe {
+
+// ---------------------------------------------------------------------------
+// Resident ("re-tiled") MXFP4 layout of one expert matrix W[rows, K]
+// (rows = 2I for mlp1, H for mlp2; K = H or I).
+//
+// The matrix is cut into tiles of TILE_M rows x KSTAGE columns.  One tile is a
+// contiguous CHUNK_BYTES chunk, chunks ordered [m_tile][k_stage], so a GEMM CTA
+// streams its weights with one bulk copy per pipeline stage:
+//
+//   [0    , 2048)  plane 0: row r's MXFP4 block for columns [0,32)  at r*16
+//   [2048 , 4096)  plane 1: row r's MXFP4 block for columns [32,64) at r*16
+//   [4096 , 4352)  scales : row r's two e8m0 bytes at r*2
+//
+// Inside a 16-byte block the four 32-bit words each cover 8 consecutive
+// columns; the eight e2m1 codes of a word are stored with the even columns in
+// nibbles 0..3 and the odd columns in nibbles 4..7, so columns (2p, 2p+1) sit 16
+// bits apart and one shift places both into a bf16x2 register.  Every nibble
+// is still an e2m1 code and every scale an e8m0 byte: only their order differs
+// from the checkpoint layout.  Rows past the end of the matrix are zero codes.
+constexpr int TILE_M = 128;
+constexpr int KSTAGE = 64;
+constexpr int PLANE_BYTES = TILE_M * 16;
+constexpr int CHUNK_BYTES = 2 * PLANE_BYTES + TILE_M * 2;  // 4352
+constexpr int MAX_SCALE_BYTE = 128;  // largest e8m0 byte the one-multiply decode covers
+
+// Device status word (one int per handle).  0 = fine.  A bounded wait that ran
+// out stores one of these (first writer wins) and the kernel winds down.
+enum DeviceStatus : int {
+    DS_OK = 0,
+    DS_TIMEOUT_FULL_W = 0x101,    // dequant warps waiting for packed weights
+    DS_TIMEOUT_FULL_A = 0x102,    // MMA warp waiting for decoded weights
+    DS_TIMEOUT_FULL_B = 0x103,    // MMA warp waiting for the activation tile
+    DS_TIMEOUT_EMPTY = 0x104,     // producer waiting for a free stage
+    DS_TIMEOUT_TMEM_FULL = 0x105, // epilogue waiting for the accumulator
+    DS_TIMEOUT_TMEM_EMPTY = 0x106,// MMA warp waiting for a drained accumulator
+    DS_BAD_SCALE = 0x201,         // a scale byte above MAX_SCALE_BYTE was uploaded
+    DS_BAD_EXPERT = 0x202,        // router produced an expert index out of range
+};
+
+__device__ __forceinline__ void report_status(int* status, int code) {
+    if (status)
+        atomicCAS(status, 0, code);
+}
+
+// ---------------------------------------------------------------------------
+// bf16 helpers
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+    return __uint_as_float(bits16 << 16);
+}
+
+// fp32 -> bf16 bits, round to nearest even (what __float2bfloat16 does in the
+// reference, src/hip/BLAS.hip:32-40).
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float f) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return float_to_bf16_bits(lo) | (float_to_bf16_bits(hi) << 16);
+}
+
+// ---------------------------------------------------------------------------
+// In-kernel MXFP4 decode (the GEMM main loops and unpack_resident use this).
+//
+// An e2m1 code s|e1 e0|m placed with its magnitude bits at bf16 bits [8:6] is
+// the bf16 number  value * 2^-126  (exponent field = e, top mantissa bit = m;
+// e = 0 lands on the bf16 subnormals exactly as 0 / 0.5 are the e2m1
+// subnormals).  One bf16x2 multiply by 2^(scale_byte - 1) then yields
+// value * 2^(scale_byte - 127) exactly: both factors have at most two
+// significant bits.  The multiplier is representable for scale bytes 0..128.
+
+// bf16x2 multiplier for a scale byte (both halves).
+__device__ __forceinline__ uint32_t mxfp4_scale_mult(uint32_t scale_byte) {
+    return ((scale_byte + 126u) << 7) * 0x00010001u;
+}
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&a);
+    __nv_bfloat162 y = *reinterpret_cast<__nv_bfloat162*>(&b);
+    __nv_bfloat162 r = __hmul2(x, y);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Eight columns: word w (resident nibble order) -> out[p] = bf16x2 of columns
+// (2p, 2p+1), low half = even column.
+__device__ __forceinline__ void mxfp4_decode_word(uint32_t w, uint32_t mult, uint32_t out[4]) {
+    const uint32_t MAG = 0x01C001C0u, SGN = 0x80008000u;
+    uint32_t b0 = ((w << 6) & MAG) | ((w << 12) & SGN);
+    uint32_t b1 = ((w << 2) & MAG) | ((w << 8) & SGN);
+    uint32_t b2 = ((w >> 2) & MAG) | ((w << 4) & SGN);
+    uint32_t b3 = ((w >> 6) & MAG) | (w & SGN);
+    out[0] = bf16x2_mul(b0, mult);
+    out[1] = bf16x2_mul(b1, mult);
+    out[2] = bf16x2_mul(b2, mult);
+    out[3] = bf16x2_mul(b3, mult);
+}
+
+// Checkpoint word (nibble i = column i) -> resident word (even columns in the
+// low half, odd columns in the high half).
+__host__ __device__ __forceinline__ uint32_t mxfp4_retile_word(uint32_t w) {
+    uint32_t even = w & 0x0F0F0F0Fu;
+    uint32_t odd = (w >> 4) & 0x0F0F0F0Fu;
+    uint32_t lo = (even & 0xFu) | ((even >> 4) & 0xF0u) | ((even >> 8) & 0xF00u) |
+                  ((even >> 12) & 0xF000u);
+    uint32_t hi = (odd & 0xFu) | ((odd >> 4) & 0xF0u) | ((odd >> 8) & 0xF00u) |
+                  ((odd >> 12) & 0xF000u);
+    return lo | (hi << 16);
+}
+
+// Exact decode of one element for ANY scale byte, integer arithmetic only:
+// the bf16 bit pattern of LUT[code] * 2^(scale_byte-127) as the reference's
+// dequantize_fp4 produces it
+// (tools/model_export/gpt-oss-20b/export_model_bin.py:75-133), including the
+// bf16 subnormals at scale byte 0 and the overflow to inf at 254/255.
+__host__ __device__ __forceinline__ uint32_t mxfp4_decode_exact(uint32_t code, uint32_t scale_byte) {
+    uint32_t sign = (code & 8u) << 12;
+    uint32_t m = code & 7u;
+    if (m == 0)
+        return sign;
+    uint32_t mant = (m >= 2) ? (m & 1u) : 0u;
+    int biased = (int)scale_byte + ((m >= 2) ? (int)(m >> 1) - 1 : -1);
+    if (biased >= 255)
+        return sign | 0x7F80u;
+    if (biased >= 1)
+        return sign | ((uint32_t)biased << 7) | (mant << 6);
+    // subnormal result: (2 + mant) * 2^(biased - 128), unit 2^-133
+    return sign | ((2u + mant) << (biased + 5));
+}
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace moe

@@ -1,0 +1,493 @@
+// Grouped expert GEMMs on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+//   MODE 0: h[rows, I]  = SwiGLU(x[rows, H] . W1_e^T + b1_e)      (bf16 out)
+//           moe_mlp1_swiglu, src/hip/moe.hip:9-258
+//   MODE 1: y[rows, H]  = h[rows, I] . W2_e^T + b2_e              (fp32 out)
+//           moe_mlp2_store / moe_mlp2_scatter, src/hip/moe.hip:261-800
+//
+// One persistent CTA per SM walks a device-built list of (expert, m-tile,
+// n-tile) work items; no value is read back by the host (the reference sizes
+// its grids from a per-layer device->host copy, src/forward.cpp:340-345,381).
+//
+// Orientation: D[128 weight rows, N token rows] = W_tile . X_tile^T, i.e. the
+// weight tile is the UMMA A operand (M = 128 TMEM lanes) and the token rows are
+// the B operand (N = 16..256 columns), so a ragged expert only narrows N.
+//
+// Warp roles (448 threads):
+//   warp 0      producer: one bulk copy of the packed-MXFP4 chunk and one TMA
+//               tile of activations per stage
+//   warp 1      allocates tensor memory, issues tcgen05.mma, commits
+//   warps 2-9   decode packed MXFP4 -> bf16 into the 128B-swizzled A stage
+//   warps 10-13 epilogue: tcgen05.ld, bias, SwiGLU / store
+//
+// Every mbarrier wait is bounded in time; a wait that runs out records a code
+// in the handle's status word, raises a CTA-wide abort flag and all roles fall
+// through to the common exit where tensor memory is released.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_mma.cuh"  // swiglu(), find_expert()
+
+namespace moe {
+namespace tc5 {
+
+constexpr int BN = 256;                 // widest token tile (TMEM columns per accumulator)
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = TILE_M * 128;        // 128 rows x 64 bf16, SW128
+constexpr int B_STAGE_BYTES = BN * 128;            // 256 rows x 64 bf16, SW128
+constexpr int W_STAGE_BYTES = CHUNK_BYTES;         // packed chunk
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + W_STAGE_BYTES;
+constexpr int N_BARRIERS = 4 * STAGES + 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + N_BARRIERS * 8 + 64 + 1024;  // + align slack
+constexpr int THREADS = 448;
+constexpr int DEQ_WARP0 = 2, DEQ_WARPS = 8;
+constexpr int EPI_WARP0 = 10;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+struct TensorMaps {
+    CUtensorMap box[4];  // token-row boxes of 32, 64, 128, 256 rows x 64 columns
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false when the time limit passed or another role has
+// raised the abort flag; the first to time out records `code`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
+                                          volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity))
+        return true;
+    unsigned long long t_start = 0;
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if ((it & 127u) == 0) {
+            if (*abort_flag)
+                return false;
+            const unsigned long long now = global_timer_ns();
+            if (t_start == 0)
+                t_start = now;
+            else if (now - t_start > WAIT_LIMIT_NS)
+                break;
+        }
+    }
+    report_status(status, code);
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] . B[smem desc]^T, bf16 x bf16 -> fp32, issued by one thread.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on `bar` when every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane
+// (taddr.lane + i), registers = columns.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float v[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+        v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major tile whose rows are 128 bytes
+// (64 bf16), 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for SW128 K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128.
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+    return (1u << 4)                       // D format fp32
+           | (1u << 7)                     // A format bf16
+           | (1u << 10)                    // B format bf16
+           | ((uint32_t)(n >> 3) << 17)    // N / 8
+           | ((uint32_t)(TILE_M >> 4) << 24);  // M / 16
+}
+
+struct TileInfo {
+    int e, mt, row0, valid_n, n_mma, box_idx, box_rows;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const int* __restrict__ g_off,
+                                                const int* __restrict__ g_cnt,
+                                                const int* __restrict__ g_tile_start, int E) {
+    // tiles ordered [expert][m_tile][n_tile]: the n-tiles that share a weight
+    // chunk run on neighbouring CTAs at the same time and meet in L2
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (g_tile_start[mid] * m_tiles <= tile)
+            lo = mid;
+        else
+            hi = mid;
+    }
+    TileInfo ti;
+    ti.e = lo;
+    const int ntl = g_tile_start[lo + 1] - g_tile_start[lo];
+    const int r = tile - g_tile_start[lo] * m_tiles;
+    ti.mt = r / ntl;
+    const int n0 = (r - ti.mt * ntl) * BN;
+    ti.row0 = g_off[lo] + n0;
+    ti.valid_n = min(BN, g_cnt[lo] - n0);
+    ti.n_mma = max(16, (ti.valid_n + 15) & ~15);
+    ti.box_idx = ti.n_mma <= 32 ? 0 : ti.n_mma <= 64 ? 1 : ti.n_mma <= 128 ? 2 : 3;
+    ti.box_rows = 32 << ti.box_idx;
+    return ti;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __restrict__ chunks,
+                       size_t expert_stride, int k_stages, int m_tiles,
+                       const float* __restrict__ bias, int bias_stride,
+                       const int* __restrict__ g_off, const int* __restrict__ g_cnt,
+                       const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
+                       int out_ld, int out_rows_valid, const int* __restrict__ row_dst, float alpha,
+                       float limit, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_dyn[];
+    // stage buffers need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_stage = smem;
+    unsigned char* b_stage = smem + STAGES * A_STAGE_BYTES;
+    unsigned char* w_stage = b_stage + STAGES * B_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_stage + STAGES * W_STAGE_BYTES);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + N_BARRIERS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar_full_w = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto bar_full_b = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
+    auto bar_full_a = [&](int s) { return bar0 + 8u * (uint32_t)(2 * STAGES + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(3 * STAGES + s); };
+    auto bar_tmem_full = [&](int b) { return bar0 + 8u * (uint32_t)(4 * STAGES + b); };
+    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(4 * STAGES + 2 + b); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full_w(s), 1);
+            mbar_init(bar_full_b(s), 1);
+            mbar_init(bar_full_a(s), DEQ_WARPS * 32);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar_tmem_full(b), 1);
+            mbar_init(bar_tmem_empty(b), 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1)
+        tmem_alloc(smem_u32(tmem_holder), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int total_tiles = g_tile_start[E] * m_tiles;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            int armed = 0;  // stages armed and not yet known complete (for the abort drain)
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const TileInfo ti = decode_tile(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const uint8_t* wsrc = chunks + (size_t)ti.e * expert_stride +
+                                      (size_t)ti.mt * k_stages * CHUNK_BYTES;
+                for (int ks = 0; ks < k_stages; ks++) {
+                    ok = mbar_wait(bar_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                    if (!ok)
+                        break;
+                    mbar_expect_tx(bar_full_w(s), W_STAGE_BYTES);
+                    bulk_load(smem_u32(w_stage + s * W_STAGE_BYTES), wsrc + (size_t)ks * CHUNK_BYTES,
+                              W_STAGE_BYTES, bar_full_w(s));
+                    mbar_expect_tx(bar_full_b(s), (uint32_t)ti.box_rows * 128u);
+                    tma_load_2d(smem_u32(b_stage + s * B_STAGE_BYTES), &maps.box[ti.box_idx],
+                                bar_full_b(s), ks * KSTAGE, ti.row0);
+                    armed = min(armed + 1, STAGES);
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // give the copies already issued a bounded time to land before the
+                // CTA exits: walk back over the last `armed` stages
+                int ss = s;
+                uint32_t pp = ph;
+                for (int i = 0; i < armed; i++) {
+                    if (--ss < 0) {
+                        ss = STAGES - 1;
+                        pp ^= 1u;
+                    }
+                    unsigned long long t0 = global_timer_ns();
+                    while (!(mbar_try_wait(bar_full_w(ss), pp) && mbar_try_wait(bar_full_b(ss), pp))) {
+                        if (global_timer_ns() - t0 > 100000000ull)
+                            break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ----------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const TileInfo ti = decode_tile(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const int ab = it & 1;
+                ok = mbar_wait(bar_tmem_empty(ab), (uint32_t)((it >> 1) & 1) ^ 1u, status,
+                               DS_TIMEOUT_TMEM_EMPTY, abort_flag);
+                if (!ok)
+                    break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
+                const uint32_t idesc = make_idesc(ti.n_mma);
+                for (int ks = 0; ks < k_stages; ks++) {
+                    ok = mbar_wait(bar_full_a(s), ph, status, DS_TIMEOUT_FULL_A, abort_flag) &&
+                         mbar_wait(bar_full_b(s), ph, status, DS_TIMEOUT_FULL_B, abort_flag);
+                    if (!ok)
+                        break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(a_stage + s * A_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(b_stage + s * B_STAGE_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < KSTAGE / 16; kk++) {
+                        umma_bf16(d_tmem, make_sw128_desc(a_addr + kk * 32),
+                                  make_sw128_desc(b_addr + kk * 32), idesc,
+                                  (uint32_t)((ks | kk) != 0));
+                    }
+                    umma_commit(bar_empty(s));  // frees this stage when the MMAs have read it
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (ok)
+                    umma_commit(bar_tmem_full(ab));
+            }
+        }
+    } else if (warp < EPI_WARP0) {
+        // ------------------------------ MXFP4 decode --------------------------
+        const int u = threadIdx.x - DEQ_WARP0 * 32;  // 0..255
+        const int r = u & (TILE_M - 1), b = u >> 7;
+        const uint32_t a_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (int ks = 0; ks < k_stages; ks++) {
+                ok = mbar_wait(bar_full_w(s), ph, status, DS_TIMEOUT_FULL_W, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                const unsigned char* wst = w_stage + s * W_STAGE_BYTES;
+                const uint4 q = *reinterpret_cast<const uint4*>(wst + b * PLANE_BYTES + r * 16);
+                const uint32_t mult = mxfp4_scale_mult(wst[2 * PLANE_BYTES + r * 2 + b]);
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                unsigned char* arow = a_stage + s * A_STAGE_BYTES + a_row_off;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint32_t d[4];
+                    mxfp4_decode_word(w[j], mult, d);
+                    const int chunk = (4 * b + j) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(arow + chunk * 16) = make_uint4(d[0], d[1], d[2], d[3]);
+                }
+                fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+                mbar_arrive(bar_full_a(s));
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;             // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;      // row inside the weight tile
+        bool ok = true;
+        int it = 0;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            const TileInfo ti = decode_tile(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+            const int ab = it & 1;
+            ok = mbar_wait(bar_tmem_full(ab), (uint32_t)((it >> 1) & 1), status,
+                           DS_TIMEOUT_TMEM_FULL, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            tc_fence_after();
+            const float* be = bias + (size_t)ti.e * bias_stride;
+            const int m = ti.mt * TILE_M + row;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
+            if (MODE == 0) {
+                uint16_t* h = static_cast<uint16_t*>(outp);
+                const float bm = be[m];  // 2I is a multiple of TILE_M: always in range
+                const int jf = m >> 1;   // feature of this gate/up pair
+                const bool odd = (lane & 1) != 0;
+                for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
+                    float v[32];
+                    tmem_ld_32x32(t_addr + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        // even lane = gate row, odd lane = the matching up row: the even
+                        // lane finishes columns c0+j, the odd lane columns c0+16+j
+                        const float mine_lo = v[j] + bm, mine_hi = v[j + 16] + bm;
+                        const float send = odd ? mine_lo : mine_hi;
+                        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                        const float gate = odd ? recv : mine_lo;
+                        const float up = odd ? mine_hi : recv;
+                        const int col = c0 + j + (odd ? 16 : 0);
+                        if (col < ti.valid_n && jf < out_rows_valid)
+                            h[(size_t)(ti.row0 + col) * out_ld + jf] =
+                                (uint16_t)float_to_bf16_bits(swiglu(gate, up, alpha, limit));
+                    }
+                }
+            } else {
+                float* y = static_cast<float*>(outp);
+                const bool m_ok = m < out_rows_valid;
+                const float bm = m_ok ? be[m] : 0.f;
+                for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
+                    float v[32];
+                    tmem_ld_32x32(t_addr + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int col = c0 + j;
+                        if (col < ti.valid_n && m_ok) {
+                            const int dst = row_dst ? row_dst[ti.row0 + col] : (ti.row0 + col);
+                            y[(size_t)dst * out_ld + m] = v[j] + bm;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_tmem_empty(ab));
+        }
+    }
+
+    // common exit: every role comes here, finished or aborted
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace tc5
+}  // namespace moe

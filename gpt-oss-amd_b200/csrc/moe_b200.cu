@@ -1,0 +1,728 @@
+// Host side of the C ABI declared in include/moe_b200.h.
+#include "../../include/moe_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "ep.cuh"
+#include "gemm_mma.cuh"
+#include "gemm_tc5.cuh"
+#include "mxfp4.cuh"
+#include "plan.cuh"
+#include "route.cuh"
+
+using namespace moe;
+
+namespace {
+
+std::string g_create_error;
+
+struct LayerWeights {
+    uint16_t* w_router = nullptr;  // [E, H] bf16
+    float* b_router = nullptr;     // [E]
+    uint8_t* w1 = nullptr;         // [n_local][m_tiles1][ks1][CHUNK_BYTES]
+    uint8_t* w2 = nullptr;         // [n_local][m_tiles2][ks2][CHUNK_BYTES]
+    float* bias1 = nullptr;        // [n_local, 2I]
+    float* bias2 = nullptr;        // [n_local, H]
+    bool router_set = false;
+    std::vector<char> expert_set;
+};
+
+}  // namespace
+
+struct moe_b200_handle_s {
+    moe_b200_config cfg{};
+    int first_expert = 0, n_local = 0;
+    int m_tiles1 = 0, m_tiles2 = 0, ks1 = 0, ks2 = 0;
+    size_t stride1 = 0, stride2 = 0;  // bytes per expert
+    int bn = 0;                       // token rows per GEMM n-tile
+    int n_sms = 0;
+    int rows_cap = 0;                 // rows the grouped buffers can hold
+    int nblk_cap = 0;
+    std::vector<LayerWeights> layers;
+    std::vector<void*> allocs;
+    size_t device_bytes = 0;
+
+    // routing + permutation workspace
+    int* topk_i = nullptr;
+    float* topk_w = nullptr;
+    int* blk_hist = nullptr;
+    int* blk_base = nullptr;
+    int* cnt = nullptr;         // [E] rows per (global) expert, send order
+    int* off = nullptr;         // [E+1]
+    int* tile_start = nullptr;  // [E+1] (ep_size == 1: the GEMM tile table)
+    int* slot_of = nullptr;     // [T*K] row of each assignment in send order
+    int* row_token = nullptr;   // [T*K]
+    uint16_t* xs = nullptr;     // [T*K, H] bf16 rows sorted by expert (send order)
+    uint16_t* hbuf = nullptr;   // [rows_cap, I] bf16
+    float* ybuf = nullptr;      // [rows_cap, H] fp32
+    int* status = nullptr;
+
+    // host staging for moe_b200_forward_host
+    void* t_dev = nullptr;
+    float* out_dev = nullptr;
+    cudaStream_t own_stream = nullptr;
+
+    // upload staging (one expert matrix)
+    uint8_t* stage_blocks = nullptr;
+    uint8_t* stage_scales = nullptr;
+
+    tc5::TensorMaps maps_x{}, maps_h{};  // TMA maps over the GEMM inputs
+    bool tc5_ready = false;
+
+    ep::State ep;
+
+    // per-stage timing: event pairs for `prof_armed` forwards
+    std::vector<cudaEvent_t> prof_ev;
+    int prof_armed = 0, prof_next = 0, prof_call = -1;
+
+    std::string err;
+    int last_launches = 0;
+};
+
+namespace {
+
+moe_b200_status fail(moe_b200_handle h, moe_b200_status st, const std::string& msg) {
+    if (h)
+        h->err = msg;
+    else
+        g_create_error = msg;
+    return st;
+}
+
+#define CU_TRY(h, expr)                                                                     \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            return fail(h, MOE_B200_ERR_CUDA,                                               \
+                        std::string(#expr) + ": " + cudaGetErrorString(_e));                \
+    } while (0)
+
+// Records the begin / end event of a stage of the forward being profiled.
+void prof_mark(moe_b200_handle h, int stage, bool begin, cudaStream_t st) {
+    if (h->prof_call < 0)
+        return;
+    cudaEventRecord(h->prof_ev[((size_t)h->prof_call * MOE_B200_N_STAGES + stage) * 2 + (begin ? 0 : 1)], st);
+}
+
+bool is_device_pointer(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+template <typename T>
+moe_b200_status dev_alloc(moe_b200_handle h, T** p, size_t n_elems) {
+    void* q = nullptr;
+    size_t bytes = n_elems * sizeof(T);
+    if (bytes == 0)
+        bytes = sizeof(T);
+    CU_TRY(h, cudaMalloc(&q, bytes));
+    h->allocs.push_back(q);
+    h->device_bytes += bytes;
+    *p = static_cast<T*>(q);
+    return MOE_B200_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+moe_b200_status make_maps(moe_b200_handle h, tc5::TensorMaps* maps, void* base, int cols, int rows) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CU_TRY(h, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess)
+        return fail(h, MOE_B200_ERR_CUDA, "cuTensorMapEncodeTiled not available in this driver");
+    EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(fn);
+    for (int i = 0; i < 4; i++) {
+        cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+        cuuint32_t box[2] = {(cuuint32_t)KSTAGE, (cuuint32_t)(32 << i)};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(&maps->box[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides,
+                            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(h, MOE_B200_ERR_CUDA,
+                        "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    }
+    return MOE_B200_OK;
+}
+
+moe_b200_status check_layer(moe_b200_handle h, int layer) {
+    if (!h)
+        return MOE_B200_ERR_INVALID;
+    if (layer < 0 || layer >= h->cfg.n_layers)
+        return fail(h, MOE_B200_ERR_INVALID, "layer index out of range");
+    return MOE_B200_OK;
+}
+
+template <int NT>
+moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int T,
+                             const LayerWeights& lw, float* score_out, int nblk, cudaStream_t st) {
+    const size_t smem = route_smem_bytes<NT>();
+    static bool attr_done = false;
+    if (!attr_done && smem > 48 * 1024) {
+        CU_TRY(h, cudaFuncSetAttribute(route_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+    }
+    attr_done = true;
+    route_kernel<NT><<<nblk, RTHREADS, smem, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T,
+                                                   h->cfg.hidden_dim, lw.w_router, lw.b_router,
+                                                   h->cfg.n_experts, h->cfg.experts_per_token,
+                                                   score_out, h->topk_i, h->topk_w, h->blk_hist);
+    return MOE_B200_OK;
+}
+
+// The two grouped GEMMs over `g_*` tables describing rows grouped by local expert.
+moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const uint16_t* xin,
+                             const tc5::TensorMaps& maps_x, int rows_upper, const int* g_off,
+                             const int* g_cnt, const int* g_tile_start, float* yout,
+                             const int* row_dst, cudaStream_t st) {
+    const moe_b200_config& c = h->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+    if (c.gemm_impl == MOE_B200_GEMM_MMA_SYNC) {
+        const int n_tiles_upper = rows_upper / V0_BN + EL;
+        dim3 g1(n_tiles_upper, h->m_tiles1), g2(n_tiles_upper, h->m_tiles2);
+        prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
+        expert_gemm_mma_kernel<0><<<g1, 256, 0, st>>>(lw.w1, h->stride1, h->ks1, lw.bias1, 2 * I, xin,
+                                                      H, g_off, g_cnt, g_tile_start, EL, h->hbuf, I,
+                                                      I, nullptr, c.swiglu_alpha, c.swiglu_limit);
+        prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
+        prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
+        expert_gemm_mma_kernel<1><<<g2, 256, 0, st>>>(lw.w2, h->stride2, h->ks2, lw.bias2, H, h->hbuf,
+                                                      I, g_off, g_cnt, g_tile_start, EL, yout, H, H,
+                                                      row_dst, c.swiglu_alpha, c.swiglu_limit);
+        prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    } else {
+        if (!h->tc5_ready) {
+            CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<0>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           tc5::SMEM_BYTES));
+            CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<1>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           tc5::SMEM_BYTES));
+            h->tc5_ready = true;
+        }
+        prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
+        tc5::expert_gemm_tc5_kernel<0><<<h->n_sms, tc5::THREADS, tc5::SMEM_BYTES, st>>>(
+            maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt,
+            g_tile_start, EL, h->hbuf, I, I, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+        prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
+        prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
+        tc5::expert_gemm_tc5_kernel<1><<<h->n_sms, tc5::THREADS, tc5::SMEM_BYTES, st>>>(
+            h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt,
+            g_tile_start, EL, yout, H, H, row_dst, c.swiglu_alpha, c.swiglu_limit, h->status);
+        prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    }
+    h->last_launches += 2;
+    return MOE_B200_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+
+extern "C" {
+
+const char* moe_b200_version(void) { return "moe_b200 0.1 sm_100a"; }
+
+void moe_b200_shard_range(int n_experts, int ep_size, int ep_rank, int* first_expert, int* n_local) {
+    // src/model.cpp:104-114: contiguous blocks, remainder to the low ranks
+    if (ep_size <= 0) {
+        if (first_expert)
+            *first_expert = 0;
+        if (n_local)
+            *n_local = 0;
+        return;
+    }
+    const int base = n_experts / ep_size, rem = n_experts % ep_size;
+    const int local = base + (ep_rank < rem ? 1 : 0);
+    const int first = ep_rank * base + (ep_rank < rem ? ep_rank : rem);
+    if (first_expert)
+        *first_expert = first;
+    if (n_local)
+        *n_local = local;
+}
+
+moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out) {
+    if (!cfg || !out)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "null argument");
+    *out = nullptr;
+    const moe_b200_config& c = *cfg;
+    if (c.hidden_dim <= 0 || c.hidden_dim % 64 || c.intermediate_dim <= 0 || c.intermediate_dim % 64)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "hidden_dim and intermediate_dim must be positive multiples of 64");
+    if (c.n_experts <= 0 || c.n_experts > 256)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "n_experts must be in 1..256");
+    if (c.experts_per_token <= 0 || c.experts_per_token > 8 || c.experts_per_token > c.n_experts)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "experts_per_token must be in 1..min(8, n_experts)");
+    if (c.n_layers <= 0 || c.max_tokens <= 0)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "n_layers and max_tokens must be positive");
+    if (c.ep_size <= 0 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.ep_size > c.n_experts)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "bad ep_rank / ep_size");
+    if (c.gemm_impl != MOE_B200_GEMM_TCGEN05 && c.gemm_impl != MOE_B200_GEMM_MMA_SYNC)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "unknown gemm_impl");
+
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
+        cudaGetLastError();
+        return fail(nullptr, MOE_B200_ERR_NO_DEVICE, "no CUDA device; this library has no CPU path");
+    }
+    if (c.device < 0 || c.device >= n_dev)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "device ordinal out of range");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, c.device) != cudaSuccess)
+        return fail(nullptr, MOE_B200_ERR_CUDA, "cudaGetDeviceProperties failed");
+    if (prop.major != 10)
+        return fail(nullptr, MOE_B200_ERR_NO_DEVICE,
+                    "device is sm_" + std::to_string(prop.major * 10 + prop.minor) +
+                        "; the kernels are built for sm_100a only");
+
+    moe_b200_handle h = new (std::nothrow) moe_b200_handle_s();
+    if (!h)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "out of host memory");
+    h->cfg = c;
+    h->n_sms = prop.multiProcessorCount;
+    moe_b200_shard_range(c.n_experts, c.ep_size, c.ep_rank, &h->first_expert, &h->n_local);
+    const int H = c.hidden_dim, I = c.intermediate_dim, E = c.n_experts, K = c.experts_per_token;
+    h->m_tiles1 = ceil_div(2 * I, TILE_M);
+    h->m_tiles2 = ceil_div(H, TILE_M);
+    h->ks1 = H / KSTAGE;
+    h->ks2 = I / KSTAGE;
+    h->stride1 = (size_t)h->m_tiles1 * h->ks1 * CHUNK_BYTES;
+    h->stride2 = (size_t)h->m_tiles2 * h->ks2 * CHUNK_BYTES;
+    h->bn = (c.gemm_impl == MOE_B200_GEMM_MMA_SYNC) ? V0_BN : tc5::BN;
+    h->rows_cap = c.max_tokens * K * c.ep_size;
+    h->nblk_cap = ceil_div(c.max_tokens, RB);
+
+    moe_b200_status st = MOE_B200_OK;
+    auto bail = [&](moe_b200_status s) {
+        std::string e = h->err;
+        moe_b200_destroy(h);
+        g_create_error = e;
+        return s;
+    };
+    if (cudaSetDevice(c.device) != cudaSuccess)
+        return bail(fail(h, MOE_B200_ERR_CUDA, "cudaSetDevice failed"));
+
+    h->layers.resize(c.n_layers);
+    for (auto& lw : h->layers) {
+        lw.expert_set.assign(h->n_local, 0);
+        if ((st = dev_alloc(h, &lw.w_router, (size_t)E * H)) || (st = dev_alloc(h, &lw.b_router, E)) ||
+            (st = dev_alloc(h, &lw.w1, h->stride1 * h->n_local)) ||
+            (st = dev_alloc(h, &lw.w2, h->stride2 * h->n_local)) ||
+            (st = dev_alloc(h, &lw.bias1, (size_t)h->n_local * 2 * I)) ||
+            (st = dev_alloc(h, &lw.bias2, (size_t)h->n_local * H)))
+            return bail(st);
+    }
+    const size_t TK = (size_t)c.max_tokens * K;
+    if ((st = dev_alloc(h, &h->topk_i, TK)) || (st = dev_alloc(h, &h->topk_w, TK)) ||
+        (st = dev_alloc(h, &h->blk_hist, (size_t)h->nblk_cap * E)) ||
+        (st = dev_alloc(h, &h->blk_base, (size_t)h->nblk_cap * E)) ||
+        (st = dev_alloc(h, &h->cnt, E)) || (st = dev_alloc(h, &h->off, E + 1)) ||
+        (st = dev_alloc(h, &h->tile_start, E + 1)) || (st = dev_alloc(h, &h->slot_of, TK)) ||
+        (st = dev_alloc(h, &h->row_token, TK)) || (st = dev_alloc(h, &h->xs, TK * H)) ||
+        (st = dev_alloc(h, &h->hbuf, (size_t)h->rows_cap * I)) ||
+        (st = dev_alloc(h, &h->ybuf, (size_t)h->rows_cap * H)) || (st = dev_alloc(h, &h->status, 1)) ||
+        (st = dev_alloc(h, (float**)&h->t_dev, (size_t)c.max_tokens * H)) ||
+        (st = dev_alloc(h, &h->out_dev, (size_t)c.max_tokens * H)) ||
+        (st = dev_alloc(h, &h->stage_blocks, (size_t)2 * I * (H / 32) * 16 > (size_t)H * (I / 32) * 16
+                                                 ? (size_t)2 * I * (H / 32) * 16
+                                                 : (size_t)H * (I / 32) * 16)) ||
+        (st = dev_alloc(h, &h->stage_scales, (size_t)2 * I * (H / 32) > (size_t)H * (I / 32)
+                                                 ? (size_t)2 * I * (H / 32)
+                                                 : (size_t)H * (I / 32))))
+        return bail(st);
+    if (cudaMemset(h->status, 0, sizeof(int)) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return bail(fail(h, MOE_B200_ERR_CUDA, "stream / memset failed"));
+    if (c.ep_size > 1) {
+        st = (moe_b200_status)ep::allocate(h->ep, c, h->n_local, h->first_expert, h->rows_cap,
+                                           h->allocs, h->device_bytes, h->err);
+        if (st)
+            return bail(st);
+    }
+    if (c.gemm_impl == MOE_B200_GEMM_TCGEN05) {
+        void* x_base = (c.ep_size > 1) ? (void*)h->ep.xgrp : (void*)h->xs;
+        const int x_rows = (c.ep_size > 1) ? h->rows_cap : (int)TK;
+        if ((st = make_maps(h, &h->maps_x, x_base, H, x_rows)) ||
+            (st = make_maps(h, &h->maps_h, h->hbuf, I, h->rows_cap)))
+            return bail(st);
+    }
+    *out = h;
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_destroy(moe_b200_handle h) {
+    if (!h)
+        return MOE_B200_OK;
+    cudaSetDevice(h->cfg.device);
+    cudaDeviceSynchronize();
+    ep::shutdown(h->ep);
+    for (void* p : h->allocs)
+        cudaFree(p);
+    for (cudaEvent_t e : h->prof_ev)
+        cudaEventDestroy(e);
+    if (h->own_stream)
+        cudaStreamDestroy(h->own_stream);
+    cudaGetLastError();
+    delete h;
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_set_router(moe_b200_handle h, int layer, const void* w_bf16,
+                                    const float* bias) {
+    moe_b200_status st = check_layer(h, layer);
+    if (st)
+        return st;
+    if (!w_bf16 || !bias)
+        return fail(h, MOE_B200_ERR_INVALID, "null router pointer");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    LayerWeights& lw = h->layers[layer];
+    const size_t E = h->cfg.n_experts, H = h->cfg.hidden_dim;
+    CU_TRY(h, cudaMemcpy(lw.w_router, w_bf16, E * H * 2, cudaMemcpyDefault));
+    CU_TRY(h, cudaMemcpy(lw.b_router, bias, E * 4, cudaMemcpyDefault));
+    lw.router_set = true;
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int first_expert, int n,
+                                           const uint8_t* blocks1, const uint8_t* scales1,
+                                           const float* bias1, const uint8_t* blocks2,
+                                           const uint8_t* scales2, const float* bias2) {
+    moe_b200_status st = check_layer(h, layer);
+    if (st)
+        return st;
+    if (!blocks1 || !scales1 || !bias1 || !blocks2 || !scales2 || !bias2)
+        return fail(h, MOE_B200_ERR_INVALID, "null expert pointer");
+    if (n <= 0 || first_expert < h->first_expert || first_expert + n > h->first_expert + h->n_local)
+        return fail(h, MOE_B200_ERR_INVALID,
+                    "experts [" + std::to_string(first_expert) + ", " +
+                        std::to_string(first_expert + n) + ") are not inside this rank's shard [" +
+                        std::to_string(h->first_expert) + ", " +
+                        std::to_string(h->first_expert + h->n_local) + ")");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    LayerWeights& lw = h->layers[layer];
+    const int H = h->cfg.hidden_dim, I = h->cfg.intermediate_dim;
+    const int G1 = H / 32, G2 = I / 32;
+    const size_t nb1 = (size_t)2 * I * G1 * 16, ns1 = (size_t)2 * I * G1;
+    const size_t nb2 = (size_t)H * G2 * 16, ns2 = (size_t)H * G2;
+    const bool dev1 = is_device_pointer(blocks1) && is_device_pointer(scales1);
+    const bool dev2 = is_device_pointer(blocks2) && is_device_pointer(scales2);
+    for (int i = 0; i < n; i++) {
+        const int le = first_expert + i - h->first_expert;
+        const uint8_t *b1 = blocks1 + i * nb1, *s1 = scales1 + i * ns1;
+        const uint8_t *b2 = blocks2 + i * nb2, *s2 = scales2 + i * ns2;
+        if (!dev1) {
+            CU_TRY(h, cudaMemcpy(h->stage_blocks, b1, nb1, cudaMemcpyHostToDevice));
+            CU_TRY(h, cudaMemcpy(h->stage_scales, s1, ns1, cudaMemcpyHostToDevice));
+            b1 = h->stage_blocks;
+            s1 = h->stage_scales;
+        }
+        mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M>>>(b1, s1, 2 * I, G1,
+                                                                   lw.w1 + le * h->stride1, h->status);
+        CU_TRY(h, cudaDeviceSynchronize());
+        if (!dev2) {
+            CU_TRY(h, cudaMemcpy(h->stage_blocks, b2, nb2, cudaMemcpyHostToDevice));
+            CU_TRY(h, cudaMemcpy(h->stage_scales, s2, ns2, cudaMemcpyHostToDevice));
+            b2 = h->stage_blocks;
+            s2 = h->stage_scales;
+        }
+        mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M>>>(b2, s2, H, G2,
+                                                                   lw.w2 + le * h->stride2, h->status);
+        CU_TRY(h, cudaDeviceSynchronize());
+        CU_TRY(h, cudaMemcpy(lw.bias1 + (size_t)le * 2 * I, bias1 + (size_t)i * 2 * I,
+                             (size_t)2 * I * 4, cudaMemcpyDefault));
+        CU_TRY(h, cudaMemcpy(lw.bias2 + (size_t)le * H, bias2 + (size_t)i * H, (size_t)H * 4,
+                             cudaMemcpyDefault));
+        lw.expert_set[le] = 1;
+    }
+    int sw = 0;
+    CU_TRY(h, cudaMemcpy(&sw, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (sw == DS_BAD_SCALE) {
+        CU_TRY(h, cudaMemset(h->status, 0, sizeof(int)));
+        for (int i = 0; i < n; i++)
+            lw.expert_set[first_expert + i - h->first_expert] = 0;
+        return fail(h, MOE_B200_ERR_UNSUPPORTED,
+                    "an e8m0 scale byte above 128 (block scale above 2) was found; the in-kernel "
+                    "decode covers scale bytes 0..128");
+    }
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, int t_dtype,
+                                 int n_tokens, float* out, int accumulate, float* router_score_out,
+                                 int* topk_i_out, float* topk_w_out, moe_b200_stream stream) {
+    moe_b200_status st = check_layer(h, layer);
+    if (st)
+        return st;
+    const moe_b200_config& c = h->cfg;
+    if (n_tokens < 0 || n_tokens > c.max_tokens)
+        return fail(h, MOE_B200_ERR_INVALID, "n_tokens outside [0, max_tokens]");
+    if (t_dtype != MOE_B200_DTYPE_F32 && t_dtype != MOE_B200_DTYPE_BF16)
+        return fail(h, MOE_B200_ERR_INVALID, "unknown activation dtype");
+    if (n_tokens > 0 && (!t || !out))
+        return fail(h, MOE_B200_ERR_INVALID, "null activation / output pointer");
+    LayerWeights& lw = h->layers[layer];
+    if (!lw.router_set)
+        return fail(h, MOE_B200_ERR_NOT_LOADED, "router weights of this layer were not set");
+    for (char s : lw.expert_set)
+        if (!s)
+            return fail(h, MOE_B200_ERR_NOT_LOADED, "not every local expert of this layer was set");
+    if (c.ep_size > 1 && !h->ep.comm)
+        return fail(h, MOE_B200_ERR_NCCL, "ep_size > 1 but moe_b200_ep_init was not called");
+    CU_TRY(h, cudaSetDevice(c.device));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int T = n_tokens, H = c.hidden_dim, E = c.n_experts, K = c.experts_per_token;
+    const int nblk = ceil_div(T, RB);
+    h->last_launches = 0;
+    h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
+
+    if (T > 0) {
+        prof_mark(h, MOE_B200_STAGE_ROUTE, true, s);
+        const int nt = ceil_div(E, 32);
+        if (nt <= 1)
+            st = launch_route<1>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
+        else if (nt <= 2)
+            st = launch_route<2>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
+        else if (nt <= 4)
+            st = launch_route<4>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
+        else
+            st = launch_route<8>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
+        if (st)
+            return st;
+        prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
+        h->last_launches++;
+    }
+    // plan + permute also run for T == 0 on an expert-parallel rank (nblk == 0
+    // gives all-zero counts), so that the collective below always has its inputs
+    prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
+    plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, h->bn, h->cnt, h->off, h->tile_start,
+                                  h->blk_base);
+    prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
+    h->last_launches++;
+    if (T > 0) {
+        prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
+        permute_kernel<<<nblk, 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, h->topk_i,
+                                            h->blk_base, h->slot_of, h->row_token, h->xs, h->status);
+        prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
+        h->last_launches++;
+    }
+
+    const float* y_for_combine = h->ybuf;
+    if (c.ep_size == 1) {
+        if (T > 0) {
+            st = launch_gemms(h, lw, h->xs, h->maps_x, T * K, h->off, h->cnt, h->tile_start, h->ybuf,
+                              nullptr, s);
+            if (st)
+                return st;
+        }
+    } else {
+        ep::GemmLauncher gl = [&](const uint16_t* xin, int rows_upper, const int* g_off,
+                                  const int* g_cnt, const int* g_tile_start, float* yout,
+                                  const int* row_dst) -> int {
+            return (int)launch_gemms(h, lw, xin, h->maps_x, rows_upper, g_off, g_cnt, g_tile_start,
+                                     yout, row_dst, s);
+        };
+        int launches = 0;
+        ep::StageMark mark = [&](int stage, bool begin) { prof_mark(h, stage, begin, s); };
+        st = (moe_b200_status)ep::exchange_and_compute(h->ep, c, h->n_local, h->first_expert, h->bn,
+                                                       T, h->cnt, h->xs, gl, mark, &y_for_combine, s,
+                                                       &launches, h->err);
+        h->last_launches += launches;
+        if (st)
+            return st;
+    }
+
+    if (T > 0) {
+        prof_mark(h, MOE_B200_STAGE_COMBINE, true, s);
+        combine_kernel<<<T, 256, 0, s>>>(y_for_combine, T, H, K, h->topk_i, h->topk_w, h->slot_of,
+                                         out, accumulate);
+        prof_mark(h, MOE_B200_STAGE_COMBINE, false, s);
+        h->last_launches++;
+        if (topk_i_out)
+            CU_TRY(h, cudaMemcpyAsync(topk_i_out, h->topk_i, (size_t)T * K * 4, cudaMemcpyDeviceToDevice, s));
+        if (topk_w_out)
+            CU_TRY(h, cudaMemcpyAsync(topk_w_out, h->topk_w, (size_t)T * K * 4, cudaMemcpyDeviceToDevice, s));
+    }
+    CU_TRY(h, cudaGetLastError());
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* t_host, int t_dtype,
+                                      int n_tokens, float* out_host, int* topk_i_host,
+                                      float* topk_w_host) {
+    moe_b200_status st = check_layer(h, layer);
+    if (st)
+        return st;
+    if (n_tokens < 0 || n_tokens > h->cfg.max_tokens)
+        return fail(h, MOE_B200_ERR_INVALID, "n_tokens outside [0, max_tokens]");
+    if (n_tokens > 0 && (!t_host || !out_host))
+        return fail(h, MOE_B200_ERR_INVALID, "null host pointer");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    const size_t H = h->cfg.hidden_dim, K = h->cfg.experts_per_token;
+    const size_t esz = (t_dtype == MOE_B200_DTYPE_F32) ? 4 : 2;
+    cudaStream_t s = h->own_stream;
+    if (n_tokens > 0)
+        CU_TRY(h, cudaMemcpyAsync(h->t_dev, t_host, (size_t)n_tokens * H * esz, cudaMemcpyHostToDevice, s));
+    st = moe_b200_forward(h, layer, h->t_dev, t_dtype, n_tokens, h->out_dev, 0, nullptr, nullptr,
+                          nullptr, reinterpret_cast<moe_b200_stream>(s));
+    if (st)
+        return st;
+    if (n_tokens > 0) {
+        CU_TRY(h, cudaMemcpyAsync(out_host, h->out_dev, (size_t)n_tokens * H * 4, cudaMemcpyDeviceToHost, s));
+        if (topk_i_host)
+            CU_TRY(h, cudaMemcpyAsync(topk_i_host, h->topk_i, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
+        if (topk_w_host)
+            CU_TRY(h, cudaMemcpyAsync(topk_w_host, h->topk_w, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
+    }
+    CU_TRY(h, cudaStreamSynchronize(s));
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_ep_unique_id(char id_out[128]) {
+    std::string err;
+    moe_b200_status st = (moe_b200_status)ep::unique_id(id_out, err);
+    if (st)
+        g_create_error = err;
+    return st;
+}
+
+moe_b200_status moe_b200_ep_init(moe_b200_handle h, const char id[128]) {
+    if (!h || !id)
+        return MOE_B200_ERR_INVALID;
+    if (h->cfg.ep_size <= 1)
+        return fail(h, MOE_B200_ERR_INVALID, "handle was created with ep_size == 1");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    return (moe_b200_status)ep::init(h->ep, id, h->cfg.ep_size, h->cfg.ep_rank, h->err);
+}
+
+void moe_b200_ep_plan(int n_experts, int ep_size, int ep_rank, const int* cnt_all, int* send_cnt,
+                      int* send_off, int* recv_cnt, int* recv_off) {
+    ep::plan_exchange(n_experts, ep_size, ep_rank, cnt_all, send_cnt, send_off, recv_cnt, recv_off);
+}
+
+size_t moe_b200_device_bytes(moe_b200_handle h) { return h ? h->device_bytes : 0; }
+
+const char* moe_b200_last_error(moe_b200_handle h) {
+    return h ? h->err.c_str() : g_create_error.c_str();
+}
+
+moe_b200_status moe_b200_device_status(moe_b200_handle h, int* status_word) {
+    if (!h || !status_word)
+        return MOE_B200_ERR_INVALID;
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    CU_TRY(h, cudaDeviceSynchronize());
+    CU_TRY(h, cudaMemcpy(status_word, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status_word != 0)
+        return fail(h, MOE_B200_ERR_DEVICE,
+                    "device status word = 0x" + [&] {
+                        char b[16];
+                        snprintf(b, sizeof b, "%x", *status_word);
+                        return std::string(b);
+                    }());
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_profile(moe_b200_handle h, int n_calls) {
+    if (!h || n_calls < 0 || n_calls > 4096)
+        return fail(h, MOE_B200_ERR_INVALID, "n_calls must be in 0..4096");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    const size_t need = (size_t)n_calls * MOE_B200_N_STAGES * 2;
+    while (h->prof_ev.size() < need) {
+        cudaEvent_t e;
+        CU_TRY(h, cudaEventCreate(&e));
+        h->prof_ev.push_back(e);
+    }
+    h->prof_armed = n_calls;
+    h->prof_next = 0;
+    h->prof_call = -1;
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_profile_read(moe_b200_handle h, int call, float* ms) {
+    if (!h || !ms || call < 0 || call >= h->prof_next)
+        return fail(h, MOE_B200_ERR_INVALID, "no profiled forward with this index");
+    for (int s = 0; s < MOE_B200_N_STAGES; s++) {
+        const size_t i = ((size_t)call * MOE_B200_N_STAGES + s) * 2;
+        float v = 0.f;
+        if (cudaEventElapsedTime(&v, h->prof_ev[i], h->prof_ev[i + 1]) != cudaSuccess) {
+            cudaGetLastError();  // stage did not run in that call
+            v = 0.f;
+        }
+        ms[s] = v;
+    }
+    return MOE_B200_OK;
+}
+
+int moe_b200_last_launch_count(moe_b200_handle h) { return h ? h->last_launches : 0; }
+
+moe_b200_status moe_b200_last_expert_counts(moe_b200_handle h, int* counts) {
+    if (!h || !counts)
+        return MOE_B200_ERR_INVALID;
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    CU_TRY(h, cudaDeviceSynchronize());
+    const int* src = (h->cfg.ep_size > 1) ? h->ep.g_cnt : h->cnt;
+    CU_TRY(h, cudaMemcpy(counts, src, (size_t)h->n_local * sizeof(int), cudaMemcpyDeviceToHost));
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_mxfp4_unpack(const uint8_t* blocks, const uint8_t* scales, long long rows,
+                                      int G, uint16_t* out_bf16, moe_b200_stream stream) {
+    if (!blocks || !scales || !out_bf16 || rows < 0 || G <= 0)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "bad argument to moe_b200_mxfp4_unpack");
+    const long long n_blocks = rows * G;
+    if (n_blocks == 0)
+        return MOE_B200_OK;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(nullptr, MOE_B200_ERR_NO_DEVICE, "no CUDA device; this library has no CPU path");
+    }
+    long long want = (n_blocks + 255) / 256;
+    int grid = (int)(want < (long long)sms * 8 ? want : (long long)sms * 8);
+    mxfp4_unpack_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(blocks, scales,
+                                                                                   n_blocks, out_bf16);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail(nullptr, MOE_B200_ERR_CUDA, cudaGetErrorString(e));
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local_expert, int which,
+                                         uint16_t* out_bf16, moe_b200_stream stream) {
+    moe_b200_status st = check_layer(h, layer);
+    if (st)
+        return st;
+    if (local_expert < 0 || local_expert >= h->n_local || (which != 1 && which != 2) || !out_bf16)
+        return fail(h, MOE_B200_ERR_INVALID, "bad argument to moe_b200_unpack_resident");
+    LayerWeights& lw = h->layers[layer];
+    if (!lw.expert_set[local_expert])
+        return fail(h, MOE_B200_ERR_NOT_LOADED, "expert was not set");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    const int H = h->cfg.hidden_dim, I = h->cfg.intermediate_dim;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (which == 1)
+        mxfp4_unpack_resident_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(
+            lw.w1 + local_expert * h->stride1, 2 * I, H, out_bf16);
+    else
+        mxfp4_unpack_resident_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(
+            lw.w2 + local_expert * h->stride2, H, I, out_bf16);
+    CU_TRY(h, cudaGetLastError());
+    return MOE_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,180 @@
+// Token -> expert permutation, tile tables for the grouped GEMMs, and the
+// routing-weighted combine.
+//
+// Replaces count_tokens_per_expert / exclusive_scan_expert_offsets /
+// compact_by_expert_kernel / gather_rows* / classify_and_build_queues
+// (src/hip/scheduler.hip:11-184), the host-side grid sizing of
+// src/forward.cpp:383-460, and the atomicAdd combine + vecadd_and_zero
+// (src/hip/moe.hip:464-509, src/hip/vecadd.hip:19-38).
+//
+// Differences by design: the order of rows inside an expert is the token order
+// (deterministic; the reference's atomic compaction is not), no value is read
+// back by the host, and the combine adds a token's K contributions in
+// ascending expert order -- the order the CPU engine uses (src/run.cpp:645-705).
+#pragma once
+#include "common.cuh"
+#include "route.cuh"
+
+namespace moe {
+
+// One block.  blk_hist [nblk, E] -> cnt[E], off[E+1] (rows sorted by expert),
+// blk_base[nblk, E] (first row of block b's assignments to expert e), and the
+// GEMM tile table tile_start[E+1] = prefix of ceil(cnt/bn).
+// Also clears counters the later kernels use.
+__global__ void __launch_bounds__(256)
+plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __restrict__ cnt,
+            int* __restrict__ off, int* __restrict__ tile_start, int* __restrict__ blk_base) {
+    __shared__ int s_cnt[256];
+    __shared__ int s_off[257];
+    const int e = threadIdx.x;
+    int total = 0;
+    if (e < E) {
+        for (int b = 0; b < nblk; b++)
+            total += blk_hist[(size_t)b * E + e];
+        s_cnt[e] = total;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, t = 0;
+        for (int i = 0; i < E; i++) {
+            s_off[i] = o;
+            off[i] = o;
+            tile_start[i] = t;
+            cnt[i] = s_cnt[i];
+            o += s_cnt[i];
+            t += (s_cnt[i] + bn - 1) / bn;
+        }
+        s_off[E] = o;
+        off[E] = o;
+        tile_start[E] = t;
+    }
+    __syncthreads();
+    if (e < E) {
+        int run = s_off[e];
+        for (int b = 0; b < nblk; b++) {
+            blk_base[(size_t)b * E + e] = run;
+            run += blk_hist[(size_t)b * E + e];
+        }
+    }
+}
+
+// Stable placement of every (token, k) assignment into its expert's row range
+// and the row gather x[token] -> xs[row] as bf16 (fp32 input is rounded here:
+// src/hip/BLAS.hip:32-40).  grid = routing blocks of RB tokens, 256 threads.
+__global__ void __launch_bounds__(256)
+permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, int E,
+               const int* __restrict__ topk_i, const int* __restrict__ blk_base,
+               int* __restrict__ slot_of, int* __restrict__ row_token,
+               uint16_t* __restrict__ xs_out, int* __restrict__ status) {
+    __shared__ int s_e[RB * 8];
+    __shared__ int s_pos[RB * 8];
+    const int t0 = blockIdx.x * RB;
+    const int n_assign = RB * K;
+    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
+        const int t = t0 + a / K;
+        int e = -1;
+        if (t < T) {
+            e = topk_i[(size_t)t0 * K + a];
+            if (e < 0 || e >= E) {
+                report_status(status, DS_BAD_EXPERT);
+                e = -1;
+            }
+        }
+        s_e[a] = e;
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
+        const int e = s_e[a];
+        int pos = -1;
+        if (e >= 0) {
+            int rank = 0;
+            for (int j = 0; j < a; j++)
+                rank += (s_e[j] == e);
+            pos = blk_base[(size_t)blockIdx.x * E + e] + rank;
+            slot_of[(size_t)t0 * K + a] = pos;
+            row_token[pos] = t0 + a / K;
+        }
+        s_pos[a] = pos;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int vec_per_row = H / 8;  // 8 bf16 = 16 bytes
+    for (int a = warp; a < n_assign; a += nwarps) {
+        const int pos = s_pos[a];
+        if (pos < 0)
+            continue;
+        const int t = t0 + a / K;
+        uint4* dst = reinterpret_cast<uint4*>(xs_out + (size_t)pos * H);
+        if (x_is_f32) {
+            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)t * H);
+            for (int v = lane; v < vec_per_row; v += 32) {
+                float4 p = src[2 * v], q = src[2 * v + 1];
+                dst[v] = make_uint4(pack_bf16x2(p.x, p.y), pack_bf16x2(p.z, p.w),
+                                    pack_bf16x2(q.x, q.y), pack_bf16x2(q.z, q.w));
+            }
+        } else {
+            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + (size_t)t * H);
+            for (int v = lane; v < vec_per_row; v += 32)
+                dst[v] = src[v];
+        }
+    }
+}
+
+// out[t,:] (+)= sum over the token's K assignments, ascending expert index, of
+// topk_w * y[slot,:].  One block per token.
+__global__ void __launch_bounds__(256)
+combine_kernel(const float* __restrict__ y, int T, int H, int K, const int* __restrict__ topk_i,
+               const float* __restrict__ topk_w, const int* __restrict__ slot_of,
+               float* __restrict__ out, int accumulate) {
+    const int t = blockIdx.x;
+    if (t >= T)
+        return;
+    int ex[8], sl[8];
+    float wt[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        if (k < K) {
+            ex[k] = topk_i[(size_t)t * K + k];
+            sl[k] = slot_of[(size_t)t * K + k];
+            wt[k] = topk_w[(size_t)t * K + k];
+        } else {
+            ex[k] = 0x7fffffff;
+            sl[k] = 0;
+            wt[k] = 0.f;
+        }
+    }
+    // sort by expert index (K <= 8): odd-even transposition network on registers
+#pragma unroll
+    for (int pass = 0; pass < 8; pass++) {
+#pragma unroll
+        for (int i = (pass & 1); i + 1 < 8; i += 2) {
+            if (ex[i] > ex[i + 1]) {
+                int te = ex[i]; ex[i] = ex[i + 1]; ex[i + 1] = te;
+                int ts = sl[i]; sl[i] = sl[i + 1]; sl[i + 1] = ts;
+                float tw = wt[i]; wt[i] = wt[i + 1]; wt[i + 1] = tw;
+            }
+        }
+    }
+    const int nvec = H / 4;
+    float4* o = reinterpret_cast<float4*>(out + (size_t)t * H);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            if (k < K) {
+                const float4 yv = reinterpret_cast<const float4*>(y + (size_t)sl[k] * H)[v];
+                acc.x = fmaf(yv.x, wt[k], acc.x);
+                acc.y = fmaf(yv.y, wt[k], acc.y);
+                acc.z = fmaf(yv.z, wt[k], acc.z);
+                acc.w = fmaf(yv.w, wt[k], acc.w);
+            }
+        }
+        if (accumulate) {
+            float4 p = o[v];
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
+        o[v] = acc;
+    }
+}
+
+}  // namespace moe

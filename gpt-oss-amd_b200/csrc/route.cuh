@@ -1,0 +1,251 @@
+// Router GEMM + bias, top-k, softmax over the selected logits, and the
+// per-block expert histogram -- one kernel.
+//
+// Replaces gemm_router (src/hip/gemms/gemm_router.hip:7-190), topk_kernel
+// (src/hip/topk.hip:5-57), softmax_kernel (src/hip/softmax.hip:5-44) and the
+// histogram half of count_tokens_per_expert (src/hip/scheduler.hip:11-31).
+//
+// Numerics.  The expert indices must equal those of the CPU engine, which sums
+// float products in a double (src/run.cpp:341-354), for every token whose
+// top-(K+1) logits are not within 1e-6 of each other.  Activations and router
+// weights are bf16, so each product is exact in fp32; the sum is formed as
+// fp32 FMA chains of RKC terms whose results are added in double and rounded
+// to fp32 once, then the fp32 bias is added (src/run.cpp:635-637).  The error
+// left is a few 1e-8, far inside the tie window.  Ties go to the lower expert
+// index (src/hip/topk.hip:30-49).
+#pragma once
+#include "common.cuh"
+
+namespace moe {
+
+constexpr int RB = 64;         // tokens per routing block
+constexpr int RKC = 32;        // K chunk
+constexpr int RLD = RKC + 4;   // padded row length in floats (conflict-free float4 reads)
+constexpr int RTHREADS = 256;
+
+template <int NT>
+constexpr size_t route_smem_bytes() {
+    size_t gemm = (size_t)(RB + NT * 32) * RLD * sizeof(float);
+    size_t logits = (size_t)RB * (NT * 32) * sizeof(float);
+    return (gemm > logits ? gemm : logits) + 256 * sizeof(int);
+}
+
+__device__ __forceinline__ void load8_as_bf16_floats(const void* base, size_t elem_off, bool f32,
+                                                     bool valid, float out[8]) {
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            out[i] = 0.f;
+        return;
+    }
+    if (f32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem_off);
+        float4 a = p[0], b = p[1];
+        float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            out[i] = bf16_bits_to_float(float_to_bf16_bits(v[i]));
+    } else {
+        uint4 q = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem_off);
+        uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+}
+
+// NT = number of 32-expert tiles (E <= 32*NT).
+template <int NT>
+__global__ void __launch_bounds__(RTHREADS)
+route_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
+             const uint16_t* __restrict__ w_router, const float* __restrict__ b_router, int E, int K,
+             float* __restrict__ score_out, int* __restrict__ topk_i, float* __restrict__ topk_w,
+             int* __restrict__ blk_hist) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* xs = reinterpret_cast<float*>(smem_raw);  // [RB][RLD]
+    float* ws = xs + RB * RLD;                       // [NT*32][RLD]
+    float* lg = reinterpret_cast<float*>(smem_raw);  // [RB][NT*32], reuses xs/ws after the GEMM
+    constexpr size_t gemm_b = (size_t)(RB + NT * 32) * RLD * sizeof(float);
+    constexpr size_t lg_b = (size_t)RB * (NT * 32) * sizeof(float);
+    int* hist = reinterpret_cast<int*>(smem_raw + (gemm_b > lg_b ? gemm_b : lg_b));
+
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * RB;
+    const int tp = tid >> 3, eq = tid & 7;
+    const bool f32 = x_is_f32 != 0;
+
+    for (int i = tid; i < 256; i += RTHREADS)
+        hist[i] = 0;
+
+    float acc[2][NT * 4];
+    double tot[2][NT * 4];
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int j = 0; j < NT * 4; j++) {
+            acc[a][j] = 0.f;
+            tot[a][j] = 0.0;
+        }
+
+    // staging registers for the next chunk
+    constexpr int WSEG = (NT * 128 + RTHREADS - 1) / RTHREADS;  // 16-byte w segments per thread
+    float xr[8];
+    float wr[WSEG][8];
+    const int xrow = tid >> 2, xseg = tid & 3;
+    auto fetch = [&](int k0) {
+        load8_as_bf16_floats(x, (size_t)(t0 + xrow) * H + k0 + xseg * 8, f32, (t0 + xrow) < T, xr);
+#pragma unroll
+        for (int s = 0; s < WSEG; s++) {
+            int seg = tid + s * RTHREADS;
+            int row = seg >> 2, sg = seg & 3;
+            bool ok = (seg < NT * 128) && (row < E);
+            load8_as_bf16_floats(w_router, (size_t)row * H + k0 + sg * 8, false, ok, wr[s]);
+        }
+    };
+    auto stash = [&]() {
+        float4* xd = reinterpret_cast<float4*>(xs + xrow * RLD + xseg * 8);
+        xd[0] = make_float4(xr[0], xr[1], xr[2], xr[3]);
+        xd[1] = make_float4(xr[4], xr[5], xr[6], xr[7]);
+#pragma unroll
+        for (int s = 0; s < WSEG; s++) {
+            int seg = tid + s * RTHREADS;
+            if (seg < NT * 128) {
+                int row = seg >> 2, sg = seg & 3;
+                float4* wd = reinterpret_cast<float4*>(ws + row * RLD + sg * 8);
+                wd[0] = make_float4(wr[s][0], wr[s][1], wr[s][2], wr[s][3]);
+                wd[1] = make_float4(wr[s][4], wr[s][5], wr[s][6], wr[s][7]);
+            }
+        }
+    };
+
+    const int n_chunks = H / RKC;
+    fetch(0);
+    for (int c = 0; c < n_chunks; c++) {
+        __syncthreads();  // previous chunk's reads done
+        stash();
+        __syncthreads();
+        if (c + 1 < n_chunks)
+            fetch((c + 1) * RKC);
+#pragma unroll
+        for (int k4 = 0; k4 < RKC / 4; k4++) {
+            const float4 xa = *reinterpret_cast<const float4*>(xs + (2 * tp) * RLD + k4 * 4);
+            const float4 xb = *reinterpret_cast<const float4*>(xs + (2 * tp + 1) * RLD + k4 * 4);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 wv =
+                        *reinterpret_cast<const float4*>(ws + (nt * 32 + eq + 8 * j) * RLD + k4 * 4);
+                    float a0 = acc[0][nt * 4 + j], a1 = acc[1][nt * 4 + j];
+                    a0 = fmaf(xa.x, wv.x, a0);
+                    a0 = fmaf(xa.y, wv.y, a0);
+                    a0 = fmaf(xa.z, wv.z, a0);
+                    a0 = fmaf(xa.w, wv.w, a0);
+                    a1 = fmaf(xb.x, wv.x, a1);
+                    a1 = fmaf(xb.y, wv.y, a1);
+                    a1 = fmaf(xb.z, wv.z, a1);
+                    a1 = fmaf(xb.w, wv.w, a1);
+                    acc[0][nt * 4 + j] = a0;
+                    acc[1][nt * 4 + j] = a1;
+                }
+        }
+#pragma unroll
+        for (int a = 0; a < 2; a++)
+#pragma unroll
+            for (int j = 0; j < NT * 4; j++) {
+                tot[a][j] += (double)acc[a][j];
+                acc[a][j] = 0.f;
+            }
+    }
+    __syncthreads();  // xs/ws dead; lg aliases them
+
+    constexpr int EP = NT * 32;
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int e = nt * 32 + eq + 8 * j;
+                float s = (float)tot[a][nt * 4 + j];
+                s += (e < E) ? b_router[e] : 0.f;
+                lg[(2 * tp + a) * EP + e] = (e < E) ? s : -INFINITY;
+            }
+    __syncthreads();
+
+    if (score_out) {
+        for (int i = tid; i < RB * E; i += RTHREADS) {
+            int r = i / E, e = i - r * E;
+            if (t0 + r < T)
+                score_out[(size_t)(t0 + r) * E + e] = lg[r * EP + e];
+        }
+    }
+
+    // top-K + softmax: one warp per token, RB/8 tokens per warp
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int r = warp; r < RB; r += RTHREADS / 32) {
+        const int t = t0 + r;
+        if (t >= T)
+            break;
+        float v[NT];
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+            v[j] = lg[r * EP + lane + 32 * j];
+        float sel_v[8];
+        int sel_i[8];
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+            if (kk < K) {
+                float bv = v[0];
+                int bi = lane;
+#pragma unroll
+                for (int j = 1; j < NT; j++)
+                    if (v[j] > bv) {
+                        bv = v[j];
+                        bi = lane + 32 * j;
+                    }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                    int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+                    if (ov > bv || (ov == bv && oi < bi)) {
+                        bv = ov;
+                        bi = oi;
+                    }
+                }
+                sel_v[kk] = bv;
+                sel_i[kk] = bi;
+                if ((bi & 31) == lane) {
+#pragma unroll
+                    for (int j = 0; j < NT; j++)
+                        if (j == (bi >> 5))
+                            v[j] = -INFINITY;
+                }
+            }
+        }
+        // softmax over the K selected logits (src/run.cpp:641, src/hip/softmax.hip:5-44)
+        float ex[8], sum = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++)
+            if (kk < K) {
+                ex[kk] = expf(sel_v[kk] - sel_v[0]);
+                sum += ex[kk];
+            }
+        if (lane == 0) {
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++)
+                if (kk < K) {
+                    topk_i[(size_t)t * K + kk] = sel_i[kk];
+                    topk_w[(size_t)t * K + kk] = ex[kk] / sum;
+                    atomicAdd(&hist[sel_i[kk]], 1);
+                }
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += RTHREADS)
+        blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
+}  // namespace moe

@@ -39,15 +39,17 @@ class MoEShape:
 
 @dataclasses.dataclass
 class LayerWeights:
+    """Router of one layer plus the experts [first_expert, first_expert + n)."""
     shape: MoEShape
     w_router: np.ndarray  # [E, H] uint16 (bf16 bits)
     b_router: np.ndarray  # [E] float32
-    blocks1: np.ndarray  # [E, 2I, H/32, 16] uint8
-    scales1: np.ndarray  # [E, 2I, H/32] uint8
-    bias1: np.ndarray  # [E, 2I] float32
-    blocks2: np.ndarray  # [E, H, I/32, 16] uint8
-    scales2: np.ndarray  # [E, H, I/32] uint8
-    bias2: np.ndarray  # [E, H] float32
+    blocks1: np.ndarray  # [n, 2I, H/32, 16] uint8
+    scales1: np.ndarray  # [n, 2I, H/32] uint8
+    bias1: np.ndarray  # [n, 2I] float32
+    blocks2: np.ndarray  # [n, H, I/32, 16] uint8
+    scales2: np.ndarray  # [n, H, I/32] uint8
+    bias2: np.ndarray  # [n, H] float32
+    first_expert: int = 0
 
 
 def bf16_bits(x: torch.Tensor) -> np.ndarray:
@@ -59,24 +61,16 @@ def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
     return (bits.astype(np.uint32) << 16).view(np.float32)
 
 
-def make_layer(shape: MoEShape, seed: int = 0, scale_lo: int = -8, scale_hi: int = -4,
-               zipf_s: float | None = None, zipf_gain: float = 1.0) -> LayerWeights:
-    """One layer's router + experts.  ``zipf_s`` replaces the router bias by
-    ``zipf_gain * log(pmf)`` of a Zipf(s) law over a seeded permutation of the
-    experts (the skewed-load configuration)."""
+def make_router(shape: MoEShape, seed: int = 0, zipf_s: float | None = None,
+                zipf_gain: float = 1.0):
+    """(w_router bf16 bits [E, H], b_router fp32 [E]).  ``zipf_s`` replaces the
+    bias by ``zipf_gain * log(pmf)`` of a Zipf(s) law over a seeded permutation
+    of the experts (the skewed-load configuration)."""
     g = torch.Generator(device="cpu")
     g.manual_seed(seed)
-    H, I, E = shape.hidden, shape.intermediate, shape.n_experts
+    H, E = shape.hidden, shape.n_experts
     w_router = bf16_bits(0.02 * torch.randn(E, H, generator=g))
     b_router = (0.1 * torch.randn(E, generator=g)).numpy().astype(np.float32)
-    blocks1 = torch.randint(0, 256, (E, 2 * I, H // 32, 16), generator=g, dtype=torch.uint8).numpy()
-    scales1 = (127 + torch.randint(scale_lo, scale_hi + 1, (E, 2 * I, H // 32), generator=g)).to(
-        torch.uint8).numpy()
-    bias1 = (0.01 * torch.randn(E, 2 * I, generator=g)).numpy().astype(np.float32)
-    blocks2 = torch.randint(0, 256, (E, H, I // 32, 16), generator=g, dtype=torch.uint8).numpy()
-    scales2 = (127 + torch.randint(scale_lo, scale_hi + 1, (E, H, I // 32), generator=g)).to(
-        torch.uint8).numpy()
-    bias2 = (0.01 * torch.randn(E, H, generator=g)).numpy().astype(np.float32)
     if zipf_s is not None:
         perm = torch.randperm(E, generator=g).numpy()
         pmf = 1.0 / np.arange(1, E + 1, dtype=np.float64) ** zipf_s
@@ -84,7 +78,43 @@ def make_layer(shape: MoEShape, seed: int = 0, scale_lo: int = -8, scale_hi: int
         b = np.empty(E, dtype=np.float64)
         b[perm] = zipf_gain * np.log(pmf)
         b_router = (b - b.mean()).astype(np.float32)
-    return LayerWeights(shape, w_router, b_router, blocks1, scales1, bias1, blocks2, scales2, bias2)
+    return w_router, b_router
+
+
+def make_experts(shape: MoEShape, seed: int, first: int, n: int, scale_lo: int = -8,
+                 scale_hi: int = -4):
+    """Packed experts [first, first + n).  Each expert has its own generator, so a
+    rank can build just its shard and still hold the bytes every other rank
+    would produce for the same (seed, expert)."""
+    H, I = shape.hidden, shape.intermediate
+    blocks1 = np.empty((n, 2 * I, H // 32, 16), dtype=np.uint8)
+    scales1 = np.empty((n, 2 * I, H // 32), dtype=np.uint8)
+    bias1 = np.empty((n, 2 * I), dtype=np.float32)
+    blocks2 = np.empty((n, H, I // 32, 16), dtype=np.uint8)
+    scales2 = np.empty((n, H, I // 32), dtype=np.uint8)
+    bias2 = np.empty((n, H), dtype=np.float32)
+    for i in range(n):
+        g = torch.Generator(device="cpu")
+        g.manual_seed(seed * 1_000_003 + 7919 * (first + i) + 17)
+        blocks1[i] = torch.randint(0, 256, (2 * I, H // 32, 16), generator=g, dtype=torch.uint8).numpy()
+        scales1[i] = (127 + torch.randint(scale_lo, scale_hi + 1, (2 * I, H // 32), generator=g)).to(
+            torch.uint8).numpy()
+        bias1[i] = (0.01 * torch.randn(2 * I, generator=g)).numpy()
+        blocks2[i] = torch.randint(0, 256, (H, I // 32, 16), generator=g, dtype=torch.uint8).numpy()
+        scales2[i] = (127 + torch.randint(scale_lo, scale_hi + 1, (H, I // 32), generator=g)).to(
+            torch.uint8).numpy()
+        bias2[i] = (0.01 * torch.randn(H, generator=g)).numpy()
+    return blocks1, scales1, bias1, blocks2, scales2, bias2
+
+
+def make_layer(shape: MoEShape, seed: int = 0, scale_lo: int = -8, scale_hi: int = -4,
+               zipf_s: float | None = None, zipf_gain: float = 1.0, first: int = 0,
+               n: int | None = None) -> LayerWeights:
+    """Router + experts [first, first + n) (default: all) of one layer."""
+    n = shape.n_experts - first if n is None else n
+    w_router, b_router = make_router(shape, seed, zipf_s, zipf_gain)
+    return LayerWeights(shape, w_router, b_router,
+                        *make_experts(shape, seed, first, n, scale_lo, scale_hi), first_expert=first)
 
 
 def make_tokens(n_tokens: int, hidden: int, seed: int = 0) -> np.ndarray:

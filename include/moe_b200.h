@@ -1,0 +1,210 @@
+/*
+ * moe_b200.h -- C ABI of the B200 (sm_100a) MoE feed-forward block for the
+ * gpt-oss-amd engine.
+ *
+ * The library replaces, inside the engine's forward(), the per-layer MoE block
+ * of src/forward.cpp:317-992 (router GEMM + bias, top-k, softmax over the
+ * selected logits, token->expert permutation, grouped gate/up GEMM with the
+ * clamped SwiGLU, grouped down GEMM, routing-weighted combine, and the
+ * expert-parallel exchange) and the expert part of the weight loader
+ * (src/model.cpp:104-114,365-399).  Expert weights are handed over and kept as
+ * packed MXFP4 (32-element e2m1 blocks + e8m0 scales); they are unpacked inside
+ * the GEMM kernels.  There is no CPU fallback: every entry point that computes
+ * needs a CUDA device of compute capability 10.0.
+ *
+ * Conventions
+ *   - plain C, no exceptions, nothing calls exit(): every function returns a
+ *     moe_b200_status (0 = success); moe_b200_last_error() gives the text.
+ *     (The reference's CHECK_HIP prints and exits, include/model.hpp:8-17.)
+ *   - one handle per GPU, used by one host thread at a time.
+ *   - moe_b200_forward() is asynchronous on the caller's stream.  With
+ *     ep_size == 1 it never synchronises with the host; with ep_size > 1 it
+ *     waits once per call for the per-rank row counts (the sizes of the
+ *     all-to-all), as the reference waits for its expert offsets every layer
+ *     (src/forward.cpp:340-345,381).
+ *   - all sizes are in elements unless a name says bytes.
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct moe_b200_handle_s* moe_b200_handle;
+/* ABI-identical to cudaStream_t / CUstream. */
+typedef struct CUstream_st* moe_b200_stream;
+
+typedef enum {
+    MOE_B200_OK = 0,
+    MOE_B200_ERR_INVALID = 1,     /* bad argument or configuration            */
+    MOE_B200_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed        */
+    MOE_B200_ERR_NO_DEVICE = 3,   /* no sm_100 device (there is no fallback)  */
+    MOE_B200_ERR_NOT_LOADED = 4,  /* weights of the layer were not set        */
+    MOE_B200_ERR_DEVICE = 5,      /* a kernel reported a bounded wait ran out */
+    MOE_B200_ERR_NCCL = 6,        /* an NCCL call failed                      */
+    MOE_B200_ERR_UNSUPPORTED = 7  /* valid input outside what is implemented  */
+} moe_b200_status;
+
+/* Activation element types accepted by moe_b200_forward(). */
+#define MOE_B200_DTYPE_F32 0  /* the engine's s->t buffer (include/model.hpp:113) */
+#define MOE_B200_DTYPE_BF16 1 /* already-rounded activations                      */
+
+/* Expert GEMM implementations.  TCGEN05 is the product path; MMA_SYNC is a
+ * plain warp-MMA kernel kept to cross-check it on the device. */
+#define MOE_B200_GEMM_TCGEN05 0
+#define MOE_B200_GEMM_MMA_SYNC 1
+
+/* Mirrors the MoE-related fields of OssConfig (include/model.hpp:25-48) plus
+ * the expert-parallel placement of OssTransformerHybrid (include/model.hpp:
+ * 232-237). */
+typedef struct {
+    int hidden_dim;        /* H, multiple of 64                                */
+    int intermediate_dim;  /* I, multiple of 64                                */
+    int n_experts;         /* E, global, <= 256                                */
+    int experts_per_token; /* K, <= 8                                          */
+    int n_layers;          /* layers held by this handle                       */
+    float swiglu_alpha;    /* 1.702 in the reference (src/run.cpp:673)         */
+    float swiglu_limit;    /* OssConfig.swiglu_limit                           */
+    int max_tokens;        /* OssConfig.batch_size: most tokens per call, per rank */
+    int ep_rank;           /* this GPU's shard, 0 <= ep_rank < ep_size         */
+    int ep_size;           /* 1 = all experts local                            */
+    int device;            /* CUDA device ordinal                              */
+    int gemm_impl;         /* MOE_B200_GEMM_*                                  */
+} moe_b200_config;
+
+/* Contiguous expert shard of a rank, remainder to the low ranks: the rule of
+ * copy_transformer_to_device (src/model.cpp:104-114).  Pure host arithmetic. */
+void moe_b200_shard_range(int n_experts, int ep_size, int ep_rank, int* first_expert,
+                          int* n_local);
+
+/* Create / destroy.  Replaces the MoE part of copy_transformer_to_device /
+ * free_transformer_on_device (src/model.cpp:59,500) and the scratch allocation
+ * of src/model.cpp:334-354: the handle owns the packed weights of its shard and
+ * a workspace sized for max_tokens; nothing is allocated afterwards. */
+moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out);
+moe_b200_status moe_b200_destroy(moe_b200_handle h);
+
+/* Router weights of one layer: w bf16 [E, H] row-major (the layout
+ * gemm_router indexes, src/hip/gemms/gemm_router.hip:91-109), bias fp32 [E].
+ * Host or device pointers.  Replaces the router part of src/model.cpp:365-399. */
+moe_b200_status moe_b200_set_router(moe_b200_handle h, int layer, const void* w_bf16,
+                                    const float* bias);
+
+/* Packed MXFP4 experts of one layer, in checkpoint layout (the input of
+ * dequantize_fp4, tools/model_export/gpt-oss-20b/export_model_bin.py:95-133):
+ *   blocks1 u8 [n, 2I, H/32, 16]  scales1 u8 [n, 2I, H/32]  bias1 f32 [n, 2I]
+ *   blocks2 u8 [n, H,  I/32, 16]  scales2 u8 [n, H,  I/32]  bias2 f32 [n, H]
+ * rows of mlp1 gate/up interleaved (src/run.cpp:667-670).  `first_expert` is a
+ * GLOBAL expert index; the n experts must lie inside this rank's shard.  Host
+ * or device pointers.  The library re-tiles the bytes for its kernels; the
+ * values they decode to are unchanged.  Scale bytes above 128 (block scales
+ * above 2) are rejected with MOE_B200_ERR_UNSUPPORTED.
+ * Replaces the expert part of src/model.cpp:141-186,365-399. */
+moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int first_expert, int n,
+                                           const uint8_t* blocks1, const uint8_t* scales1,
+                                           const float* bias1, const uint8_t* blocks2,
+                                           const uint8_t* scales2, const float* bias2);
+
+/* The MoE block of one layer for n_tokens rows (src/forward.cpp:317-514, and
+ * :515-992 when ep_size > 1).
+ *   t            device, [n_tokens, H], f32 or bf16 (f32 is rounded to bf16 on
+ *                load, as src/hip/BLAS.hip:32-40 does)
+ *   out          device f32 [n_tokens, H]; accumulate == 0: out = e_agg;
+ *                accumulate != 0: out += e_agg (the residual add of
+ *                src/hip/vecadd.hip:19-38 fused into the combine)
+ *   router_score_out / topk_i_out / topk_w_out   optional device buffers
+ *                [n_tokens, E] f32 / [n_tokens, K] i32 / [n_tokens, K] f32: the
+ *                engine's observable side buffers (include/model.hpp:132-134);
+ *                topk_w is after the softmax
+ * With ep_size > 1 every rank must call this for the same layer in the same
+ * order (n_tokens may differ per rank, 0 included). */
+moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, int t_dtype,
+                                 int n_tokens, float* out, int accumulate,
+                                 float* router_score_out, int* topk_i_out, float* topk_w_out,
+                                 moe_b200_stream stream);
+
+/* Same call with HOST buffers: t (pinned or pageable) is copied to the device,
+ * the block runs, out is copied back, and the call returns when out is valid.
+ * This is the path an engine without device-resident activations would use and
+ * the one the end-to-end figure is measured through. */
+moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* t_host,
+                                      int t_dtype, int n_tokens, float* out_host,
+                                      int* topk_i_host, float* topk_w_host);
+
+/* Expert-parallel communicator (replaces the peer-access / peer-copy set-up of
+ * src/getp/run.cpp:186-202,237-318).  Rank 0 calls moe_b200_ep_unique_id and
+ * sends the 128 bytes to the other ranks by any host channel; every rank then
+ * calls moe_b200_ep_init.  Uses NCCL (ncclCommInitRank) over NVLink. */
+moe_b200_status moe_b200_ep_unique_id(char id_out[128]);
+moe_b200_status moe_b200_ep_init(moe_b200_handle h, const char id[128]);
+
+/* The host-side plan of one expert-parallel exchange, as moe_b200_forward
+ * computes it: cnt_all [ep_size, n_experts] holds every rank's per-expert row
+ * counts (rows are sent sorted by global expert); the outputs, each [ep_size],
+ * give how many rows this rank sends to / receives from each peer and the
+ * first row of each peer's range in its send / receive buffer.  Pure host
+ * arithmetic (replaces the per-shard bookkeeping of src/forward.cpp:565-592). */
+void moe_b200_ep_plan(int n_experts, int ep_size, int ep_rank, const int* cnt_all, int* send_cnt,
+                      int* send_off, int* recv_cnt, int* recv_off);
+
+/* Bytes of device memory the handle holds (weights + workspace). */
+size_t moe_b200_device_bytes(moe_b200_handle h);
+/* Text of the last error on this handle (or of the last failed create when h
+ * is NULL).  Never NULL. */
+const char* moe_b200_last_error(moe_b200_handle h);
+/* Reads the device status word (synchronises the device): 0 = no kernel has
+ * reported a problem; otherwise a code naming the wait that ran out. */
+moe_b200_status moe_b200_device_status(moe_b200_handle h, int* status_word);
+/* Number of kernels the last moe_b200_forward launched on this handle. */
+int moe_b200_last_launch_count(moe_b200_handle h);
+/* Per-expert row counts of the last forward on this rank (device->host copy,
+ * synchronises): counts[n_local].  For load histograms in reports. */
+moe_b200_status moe_b200_last_expert_counts(moe_b200_handle h, int* counts);
+
+/* Per-stage device timing (the reference's -f profiling flag calls functions
+ * that do not exist in its tree, src/run.cpp:1208; this is the working
+ * equivalent).  moe_b200_profile(h, n_calls) arms CUDA-event pairs around the
+ * stages of the next n_calls forwards on the stream they run on (n_calls == 0
+ * disarms); after the stream has been synchronised,
+ * moe_b200_profile_read(h, call, ms) returns the milliseconds of each stage of
+ * the call-th armed forward in ms[MOE_B200_N_STAGES] (0 for a stage that did
+ * not run). */
+#define MOE_B200_STAGE_ROUTE 0    /* router GEMM + top-k + softmax           */
+#define MOE_B200_STAGE_PLAN 1     /* offsets, tile table                     */
+#define MOE_B200_STAGE_PERMUTE 2  /* row gather into expert order            */
+#define MOE_B200_STAGE_DISPATCH 3 /* counts all-gather + row all-to-all (EP) */
+#define MOE_B200_STAGE_REGROUP 4  /* received rows grouped by expert (EP)    */
+#define MOE_B200_STAGE_GEMM1 5    /* gate/up GEMM + SwiGLU                   */
+#define MOE_B200_STAGE_GEMM2 6    /* down GEMM                               */
+#define MOE_B200_STAGE_RETURN 7   /* result all-to-all (EP)                  */
+#define MOE_B200_STAGE_COMBINE 8  /* routing-weighted combine                */
+#define MOE_B200_N_STAGES 9
+moe_b200_status moe_b200_profile(moe_b200_handle h, int n_calls);
+moe_b200_status moe_b200_profile_read(moe_b200_handle h, int call, float* ms);
+
+/* MXFP4 -> bf16 on the device, checkpoint layout in, row-major bf16 out:
+ * blocks [rows, G, 16], scales [rows, G] -> out [rows, 32*G] (bf16 bits).
+ * Bit-exact with dequantize_fp4 for every scale byte
+ * (tools/model_export/gpt-oss-20b/export_model_bin.py:95-133).  Device
+ * pointers. */
+moe_b200_status moe_b200_mxfp4_unpack(const uint8_t* blocks, const uint8_t* scales, long long rows,
+                                      int G, uint16_t* out_bf16, moe_b200_stream stream);
+
+/* Decodes the RESIDENT (re-tiled) weights of one local expert with the same
+ * device function the GEMM main loop uses, to row-major bf16:
+ * which == 1 -> [2I, H], which == 2 -> [H, I].  For bit-exactness tests of the
+ * in-kernel unpack.  Device pointer out. */
+moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local_expert, int which,
+                                         uint16_t* out_bf16, moe_b200_stream stream);
+
+/* Library build info, e.g. "moe_b200 0.1 sm_100a". */
+const char* moe_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H */

@@ -122,26 +122,59 @@ class ExpertCache:
     """fp32 (decoded) weights of the experts a batch touches, decoded on demand
     from packed MXFP4 so full-size layers need not be expanded whole."""
 
-    def __init__(self, blocks1, scales1, bias1, blocks2, scales2, bias2):
-        self.blocks1, self.scales1, self.bias1 = blocks1, scales1, bias1
-        self.blocks2, self.scales2, self.bias2 = blocks2, scales2, bias2
-        self.E = blocks1.shape[0]
+    def __init__(self, blocks1, scales1, bias1, blocks2, scales2, bias2, first_expert=0,
+                 loader=None):
+        """Arrays hold experts [first_expert, first_expert + n).  ``loader(e)``,
+        if given, supplies the six packed arrays of a single expert that is not
+        in the arrays (used when a full layer is too large to keep packed)."""
+        self.blocks1, self.scales1, self._bias1 = blocks1, scales1, bias1
+        self.blocks2, self.scales2, self._bias2 = blocks2, scales2, bias2
+        self.first = first_expert
+        self.loader = loader
+        self.intermediate = (blocks2.shape[2] * 32) if blocks2 is not None else None
         self._w1 = {}
         self._w2 = {}
+        self._b = {}
+
+    def _have(self, e):
+        return self.blocks1 is not None and self.first <= e < self.first + self.blocks1.shape[0]
+
+    def _load(self, e):
+        if e in self._w1:
+            return
+        if self._have(e):
+            i = e - self.first
+            b1, s1, c1, b2, s2, c2 = (self.blocks1[i], self.scales1[i], self._bias1[i],
+                                      self.blocks2[i], self.scales2[i], self._bias2[i])
+        else:
+            b1, s1, c1, b2, s2, c2 = (a[0] for a in self.loader(e))
+        self._w1[e] = mxfp4_dequant_f32(b1, s1)
+        self._w2[e] = mxfp4_dequant_f32(b2, s2)
+        self._b[e] = (np.ascontiguousarray(c1, dtype=np.float32),
+                      np.ascontiguousarray(c2, dtype=np.float32))
+        if self.intermediate is None:
+            self.intermediate = self._w2[e].shape[1]
 
     def w1(self, e):
-        if e not in self._w1:
-            self._w1[e] = mxfp4_dequant_f32(self.blocks1[e], self.scales1[e])
+        self._load(e)
         return self._w1[e]
 
     def w2(self, e):
-        if e not in self._w2:
-            self._w2[e] = mxfp4_dequant_f32(self.blocks2[e], self.scales2[e])
+        self._load(e)
         return self._w2[e]
+
+    def bias1(self, e):
+        self._load(e)
+        return self._b[e][0]
+
+    def bias2(self, e):
+        self._load(e)
+        return self._b[e][1]
 
     def drop(self):
         self._w1.clear()
         self._w2.clear()
+        self._b.clear()
 
 
 def route(x_f32, w_router_f32, b_router, top_k, round_mode=1):
@@ -168,7 +201,6 @@ def moe_forward(x_f32, w_router_f32, b_router, experts: ExpertCache, top_k=4, al
     br = np.ascontiguousarray(b_router, dtype=np.float32)
     T, H = x.shape
     E = wr.shape[0]
-    I = experts.blocks2.shape[2] * 32
     _, ti, _ = route(x, wr, br, top_k, round_mode)
     needed = sorted(set(int(e) for e in ti.reshape(-1)))
     PtrArr = ctypes.c_void_p * E
@@ -176,11 +208,11 @@ def moe_forward(x_f32, w_router_f32, b_router, experts: ExpertCache, top_k=4, al
     keep = []
     for e in needed:
         w1, w2 = experts.w1(e), experts.w2(e)
-        b1 = np.ascontiguousarray(experts.bias1[e], dtype=np.float32)
-        b2 = np.ascontiguousarray(experts.bias2[e], dtype=np.float32)
+        b1, b2 = experts.bias1(e), experts.bias2(e)
         keep += [w1, w2, b1, b2]
         w1p[e], b1p[e], w2p[e], b2p[e] = (w1.ctypes.data, b1.ctypes.data, w2.ctypes.data,
                                           b2.ctypes.data)
+    I = experts.intermediate
     scores = np.empty((T, E), dtype=np.float32)
     topk_i = np.empty((T, top_k), dtype=np.int32)
     topk_v = np.empty((T, top_k), dtype=np.float32)
