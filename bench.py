@@ -145,6 +145,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "mma_sync"])
     ap.add_argument("--cpu-sample", type=int, default=16, help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override the workload's tokens per step (for small profiling captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -153,7 +155,9 @@ def main():
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     warmup = max(args.warmup, 3)
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.tokens > 0:
+        wl["T"] = args.tokens
 
     import gpt_oss_amd_b200 as pkg
     from gpt_oss_amd_b200 import capi, synth

@@ -22,6 +22,7 @@ SYMBOLS = [
     "moe_b200_last_error", "moe_b200_device_status", "moe_b200_last_launch_count",
     "moe_b200_last_expert_counts", "moe_b200_mxfp4_unpack", "moe_b200_unpack_resident",
     "moe_b200_version", "moe_b200_profile", "moe_b200_profile_read",
+    "moe_b200_last_intermediate",
 ]
 N_STAGES = 9
 STAGE_NAMES = ["route", "plan", "permute", "dispatch", "regroup", "gemm1", "gemm2", "return",
@@ -82,6 +83,7 @@ def lib() -> ctypes.CDLL:
         L.moe_b200_mxfp4_unpack.argtypes = [vp, vp, ctypes.c_longlong, ci, vp, vp]
         L.moe_b200_unpack_resident.argtypes = [vp, ci, ci, ci, vp, vp]
         L.moe_b200_version.restype = ctypes.c_char_p
+        L.moe_b200_last_intermediate.argtypes = [vp, ci, vp, vp]
         L.moe_b200_profile.argtypes = [vp, ci]
         L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
         _lib = L

@@ -169,9 +169,30 @@ moe_b200_status check_layer(moe_b200_handle h, int layer) {
     return MOE_B200_OK;
 }
 
+// Batches up to this many tokens are routed by the warp-per-token kernel (RBS
+// tokens per block) so that a decode-sized batch still spreads over the GPU.
+constexpr int ROUTE_SMALL_MAX_TOKENS = 2048;
+
+int route_block_tokens(int T, int H) {
+    return (T <= ROUTE_SMALL_MAX_TOKENS && route_small_smem_bytes(H) <= 200 * 1024) ? RBS : RB;
+}
+
 template <int NT>
 moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int T,
                              const LayerWeights& lw, float* score_out, int nblk, cudaStream_t st) {
+    if (route_block_tokens(T, h->cfg.hidden_dim) == RBS) {
+        const size_t smem = route_small_smem_bytes(h->cfg.hidden_dim);
+        static size_t attr_smem = 0;
+        if (smem > attr_smem) {
+            CU_TRY(h, cudaFuncSetAttribute(route_small_kernel<NT>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_smem = smem;
+        }
+        route_small_kernel<NT><<<nblk, RBS * 32, smem, st>>>(
+            t, t_dtype == MOE_B200_DTYPE_F32, T, h->cfg.hidden_dim, lw.w_router, lw.b_router,
+            h->cfg.n_experts, h->cfg.experts_per_token, score_out, h->topk_i, h->topk_w, h->blk_hist);
+        return MOE_B200_OK;
+    }
     const size_t smem = route_smem_bytes<NT>();
     static bool attr_done = false;
     if (!attr_done && smem > 48 * 1024) {
@@ -305,7 +326,11 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
     h->stride2 = (size_t)h->m_tiles2 * h->ks2 * CHUNK_BYTES;
     h->bn = (c.gemm_impl == MOE_B200_GEMM_MMA_SYNC) ? V0_BN : tc5::BN;
     h->rows_cap = c.max_tokens * K * c.ep_size;
-    h->nblk_cap = ceil_div(c.max_tokens, RB);
+    {
+        const int small = c.max_tokens < ROUTE_SMALL_MAX_TOKENS ? c.max_tokens : ROUTE_SMALL_MAX_TOKENS;
+        const int a = ceil_div(c.max_tokens, RB), b = ceil_div(small, RBS);
+        h->nblk_cap = a > b ? a : b;
+    }
 
     moe_b200_status st = MOE_B200_OK;
     auto bail = [&](moe_b200_status s) {
@@ -486,7 +511,8 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     CU_TRY(h, cudaSetDevice(c.device));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int T = n_tokens, H = c.hidden_dim, E = c.n_experts, K = c.experts_per_token;
-    const int nblk = ceil_div(T, RB);
+    const int rb = route_block_tokens(T, H);
+    const int nblk = ceil_div(T, rb);
     h->last_launches = 0;
     h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
 
@@ -515,8 +541,9 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     h->last_launches++;
     if (T > 0) {
         prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
-        permute_kernel<<<nblk, 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, h->topk_i,
-                                            h->blk_base, h->slot_of, h->row_token, h->xs, h->status);
+        permute_kernel<<<nblk, 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb,
+                                            h->topk_i, h->blk_base, h->slot_of, h->row_token, h->xs,
+                                            h->status);
         prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
         h->last_launches++;
     }
@@ -699,6 +726,23 @@ moe_b200_status moe_b200_mxfp4_unpack(const uint8_t* blocks, const uint8_t* scal
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
         return fail(nullptr, MOE_B200_ERR_CUDA, cudaGetErrorString(e));
+    return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_last_intermediate(moe_b200_handle h, int n_tokens, uint16_t* out_bf16,
+                                           moe_b200_stream stream) {
+    if (!h || !out_bf16 || n_tokens < 0 || n_tokens > h->cfg.max_tokens)
+        return fail(h, MOE_B200_ERR_INVALID, "bad argument to moe_b200_last_intermediate");
+    if (h->cfg.ep_size != 1)
+        return fail(h, MOE_B200_ERR_UNSUPPORTED, "only available with ep_size == 1");
+    const int rows = n_tokens * h->cfg.experts_per_token;
+    if (rows == 0)
+        return MOE_B200_OK;
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    int blocks = (rows + 7) / 8;
+    ep::regroup_rows_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        h->hbuf, h->slot_of, rows, h->cfg.intermediate_dim, out_bf16);
+    CU_TRY(h, cudaGetLastError());
     return MOE_B200_OK;
 }
 

@@ -62,14 +62,14 @@ plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __re
 // and the row gather x[token] -> xs[row] as bf16 (fp32 input is rounded here:
 // src/hip/BLAS.hip:32-40).  grid = routing blocks of RB tokens, 256 threads.
 __global__ void __launch_bounds__(256)
-permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, int E,
+permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, int E, int rb,
                const int* __restrict__ topk_i, const int* __restrict__ blk_base,
                int* __restrict__ slot_of, int* __restrict__ row_token,
                uint16_t* __restrict__ xs_out, int* __restrict__ status) {
     __shared__ int s_e[RB * 8];
     __shared__ int s_pos[RB * 8];
-    const int t0 = blockIdx.x * RB;
-    const int n_assign = RB * K;
+    const int t0 = blockIdx.x * rb;  // rb <= RB tokens per block, the routing kernel's block size
+    const int n_assign = rb * K;
     for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
         const int t = t0 + a / K;
         int e = -1;

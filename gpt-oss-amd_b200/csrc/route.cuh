@@ -56,6 +56,65 @@ __device__ __forceinline__ void load8_as_bf16_floats(const void* base, size_t el
     }
 }
 
+// One warp: v[j] holds the logit of expert lane + 32 j (-inf past E).  Selects
+// the K largest (ties to the lower index, src/hip/topk.hip:30-49), applies the
+// softmax over the selected logits (src/run.cpp:641, src/hip/softmax.hip:5-44),
+// stores indices and weights of token t and counts the experts in `hist`
+// (shared memory, integer adds: order-independent).
+template <int NT>
+__device__ __forceinline__ void select_topk_softmax(float v[NT], int lane, int K, int t,
+                                                    int* __restrict__ topk_i,
+                                                    float* __restrict__ topk_w, int* hist) {
+    float sel_v[8];
+    int sel_i[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; kk++) {
+        if (kk < K) {
+            float bv = v[0];
+            int bi = lane;
+#pragma unroll
+            for (int j = 1; j < NT; j++)
+                if (v[j] > bv) {
+                    bv = v[j];
+                    bi = lane + 32 * j;
+                }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+                if (ov > bv || (ov == bv && oi < bi)) {
+                    bv = ov;
+                    bi = oi;
+                }
+            }
+            sel_v[kk] = bv;
+            sel_i[kk] = bi;
+            if ((bi & 31) == lane) {
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+                    if (j == (bi >> 5))
+                        v[j] = -INFINITY;
+            }
+        }
+    }
+    float ex[8], sum = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 8; kk++)
+        if (kk < K) {
+            ex[kk] = expf(sel_v[kk] - sel_v[0]);
+            sum += ex[kk];
+        }
+    if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++)
+            if (kk < K) {
+                topk_i[(size_t)t * K + kk] = sel_i[kk];
+                topk_w[(size_t)t * K + kk] = ex[kk] / sum;
+                atomicAdd(&hist[sel_i[kk]], 1);
+            }
+    }
+}
+
 // NT = number of 32-expert tiles (E <= 32*NT).
 template <int NT>
 __global__ void __launch_bounds__(RTHREADS)
@@ -193,58 +252,124 @@ route_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
 #pragma unroll
         for (int j = 0; j < NT; j++)
             v[j] = lg[r * EP + lane + 32 * j];
-        float sel_v[8];
-        int sel_i[8];
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++) {
-            if (kk < K) {
-                float bv = v[0];
-                int bi = lane;
-#pragma unroll
-                for (int j = 1; j < NT; j++)
-                    if (v[j] > bv) {
-                        bv = v[j];
-                        bi = lane + 32 * j;
-                    }
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-                    float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-                    int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-                    if (ov > bv || (ov == bv && oi < bi)) {
-                        bv = ov;
-                        bi = oi;
-                    }
-                }
-                sel_v[kk] = bv;
-                sel_i[kk] = bi;
-                if ((bi & 31) == lane) {
-#pragma unroll
-                    for (int j = 0; j < NT; j++)
-                        if (j == (bi >> 5))
-                            v[j] = -INFINITY;
-                }
-            }
-        }
-        // softmax over the K selected logits (src/run.cpp:641, src/hip/softmax.hip:5-44)
-        float ex[8], sum = 0.f;
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++)
-            if (kk < K) {
-                ex[kk] = expf(sel_v[kk] - sel_v[0]);
-                sum += ex[kk];
-            }
-        if (lane == 0) {
-#pragma unroll
-            for (int kk = 0; kk < 8; kk++)
-                if (kk < K) {
-                    topk_i[(size_t)t * K + kk] = sel_i[kk];
-                    topk_w[(size_t)t * K + kk] = ex[kk] / sum;
-                    atomicAdd(&hist[sel_i[kk]], 1);
-                }
-        }
+        select_topk_softmax<NT>(v, lane, K, t, topk_i, topk_w, hist);
     }
     __syncthreads();
     for (int e = tid; e < E; e += RTHREADS)
+        blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
+// ---------------------------------------------------------------------------
+// Small-batch variant: RBS tokens per block, one warp per token, so that a
+// decode-sized batch (a few hundred tokens) still fills the GPU.  The token rows
+// and eight router rows at a time sit in shared memory as bf16; every lane owns
+// the 16-byte vectors lane, lane+32, ... of the K axis and keeps eight fp32
+// partial sums (chains of H/32 exact products), which a shuffle tree adds.
+constexpr int RBS = 8;     // tokens (= warps) per block
+constexpr int RGE = 8;     // experts staged per pass
+
+inline size_t route_small_smem_bytes(int H) { return (size_t)(RBS + RGE) * H * 2 + 256 * sizeof(int); }
+
+template <int NT>
+__global__ void __launch_bounds__(RBS * 32)
+route_small_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
+                   const uint16_t* __restrict__ w_router, const float* __restrict__ b_router, int E,
+                   int K, float* __restrict__ score_out, int* __restrict__ topk_i,
+                   float* __restrict__ topk_w, int* __restrict__ blk_hist) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);  // [RBS][H]
+    uint16_t* ws = xs + (size_t)RBS * H;                   // [RGE][H]
+    int* hist = reinterpret_cast<int*>(ws + (size_t)RGE * H);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t0 = blockIdx.x * RBS;
+    const int vec = H / 8;
+    for (int i = tid; i < 256; i += RBS * 32)
+        hist[i] = 0;
+    // stage the block's token rows as bf16
+    for (int i = tid; i < RBS * vec; i += RBS * 32) {
+        const int r = i / vec, v = i - r * vec;
+        uint4 q = make_uint4(0, 0, 0, 0);
+        if (t0 + r < T) {
+            if (x_is_f32) {
+                const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) +
+                                                                  (size_t)(t0 + r) * H) + 2 * v;
+                const float4 a = p[0], b = p[1];
+                q = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
+                               pack_bf16x2(b.z, b.w));
+            } else {
+                q = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + (size_t)(t0 + r) * H)[v];
+            }
+        }
+        reinterpret_cast<uint4*>(xs + (size_t)r * H)[v] = q;
+    }
+    float logit[NT];
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+        logit[j] = -INFINITY;
+    const int t = t0 + warp;
+    for (int e0 = 0; e0 < E; e0 += RGE) {
+        __syncthreads();  // previous group consumed (first pass: xs staged)
+        for (int i = tid; i < RGE * vec; i += RBS * 32) {
+            const int r = i / vec, v = i - r * vec;
+            uint4 q = make_uint4(0, 0, 0, 0);
+            if (e0 + r < E)
+                q = reinterpret_cast<const uint4*>(w_router + (size_t)(e0 + r) * H)[v];
+            reinterpret_cast<uint4*>(ws + (size_t)r * H)[v] = q;
+        }
+        __syncthreads();
+        float acc[RGE];
+#pragma unroll
+        for (int g = 0; g < RGE; g++)
+            acc[g] = 0.f;
+        for (int v = lane; v < vec; v += 32) {
+            const uint4 xq = reinterpret_cast<const uint4*>(xs + (size_t)warp * H)[v];
+            const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w};
+            float xf[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                xf[2 * i] = __uint_as_float(xw[i] << 16);
+                xf[2 * i + 1] = __uint_as_float(xw[i] & 0xFFFF0000u);
+            }
+#pragma unroll
+            for (int g = 0; g < RGE; g++) {
+                const uint4 wq = reinterpret_cast<const uint4*>(ws + (size_t)g * H)[v];
+                const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
+                float a = acc[g];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    a = fmaf(xf[2 * i], __uint_as_float(ww[i] << 16), a);
+                    a = fmaf(xf[2 * i + 1], __uint_as_float(ww[i] & 0xFFFF0000u), a);
+                }
+                acc[g] = a;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < RGE; g++) {
+            float a = acc[g];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+                a += __shfl_xor_sync(0xffffffffu, a, off);
+            const int e = e0 + g;
+            if (e < E && (e & 31) == lane) {
+                const float sc = a + b_router[e];
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+                    if (j == (e >> 5))
+                        logit[j] = sc;
+            }
+        }
+    }
+    if (t < T) {
+        if (score_out) {
+#pragma unroll
+            for (int j = 0; j < NT; j++)
+                if (lane + 32 * j < E)
+                    score_out[(size_t)t * E + lane + 32 * j] = logit[j];
+        }
+        select_topk_softmax<NT>(logit, lane, K, t, topk_i, topk_w, hist);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += RBS * 32)
         blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
 }
 

@@ -153,6 +153,16 @@ class MoEEngine:
         capi.check(capi.lib().moe_b200_last_expert_counts(self._h, arr), self._h)
         return list(arr)
 
+    def last_intermediate(self, n_tokens: int) -> torch.Tensor:
+        """bf16 bits [n_tokens, K, I] of the SwiGLU output that entered the down
+        projection in the last forward (ep_size == 1)."""
+        K, I = self.shape.top_k, self.shape.intermediate
+        out = torch.empty(n_tokens, K, I, dtype=torch.int16, device=f"cuda:{self.device}")
+        s = torch.cuda.current_stream(out.device)
+        capi.check(capi.lib().moe_b200_last_intermediate(self._h, n_tokens, _ptr(out),
+                                                         ctypes.c_void_p(s.cuda_stream)), self._h)
+        return out
+
     def profile(self, n_calls: int):
         """Arm per-stage CUDA-event timing for the next n_calls forwards."""
         capi.check(capi.lib().moe_b200_profile(self._h, n_calls), self._h)

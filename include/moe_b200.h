@@ -201,6 +201,15 @@ moe_b200_status moe_b200_mxfp4_unpack(const uint8_t* blocks, const uint8_t* scal
 moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local_expert, int which,
                                          uint16_t* out_bf16, moe_b200_stream stream);
 
+/* The intermediate of the last forward (ep_size == 1 only): the bf16 SwiGLU
+ * output that entered the down projection, gathered back into assignment
+ * order: out_bf16 device [n_tokens * K, I], row t*K + k = expert topk_i[t][k].
+ * (The engine's gate_by_expert buffer, include/model.hpp:172, in token order.)
+ * Lets a test separate bf16 rounding flips of this intermediate from real
+ * errors. */
+moe_b200_status moe_b200_last_intermediate(moe_b200_handle h, int n_tokens, uint16_t* out_bf16,
+                                           moe_b200_stream stream);
+
 /* Library build info, e.g. "moe_b200 0.1 sm_100a". */
 const char* moe_b200_version(void);
 

@@ -218,13 +218,16 @@ static inline float oracle_swiglu(float gate, float up, float alpha, float limit
  *   and the SwiGLU output is rounded to bf16 before MLP2 (src/hip/moe.hip:343).
  *
  * Outputs (any may be NULL): router_score [T,E], topk_i [T,K], topk_v [T,K]
- * (after softmax), e_agg [T,H].
+ * (after softmax), e_agg [T,H], and h [T,K,I]: the SwiGLU output that enters
+ * MLP2 (after the bf16 rounding in round_mode 1) of the expert at position k of
+ * the token's top-k list -- used to tell bf16 rounding flips of h apart from
+ * real errors.
  */
 int oracle_moe_forward(int T, int H, int I, int E, int K, float alpha, float limit, int round_mode,
                        const float* t_in, const float* w_router, const float* b_router,
                        const float* const* w1, const float* const* b1, const float* const* w2,
                        const float* const* b2, float* router_score_out, int* topk_i_out,
-                       float* topk_v_out, float* e_agg_out) {
+                       float* topk_v_out, float* e_agg_out, float* h_out) {
     float* t = (float*)malloc(sizeof(float) * (size_t)H);
     float* router_score = (float*)malloc(sizeof(float) * (size_t)E);
     float* topk_v = (float*)malloc(sizeof(float) * (size_t)K);
@@ -254,10 +257,11 @@ int oracle_moe_forward(int T, int H, int I, int E, int K, float alpha, float lim
         memset(e_agg, 0, sizeof(float) * (size_t)H);
         for (int e = 0; e < E; e++) {
             float expert_w = 0;
-            int in_topk = 0;
+            int in_topk = 0, k_pos = 0;
             for (int idx = 0; idx < K; idx++) {
                 if (topk_i[idx] == e) {
                     in_topk = 1;
+                    k_pos = idx;
                     expert_w = topk_v[idx];
                     break;
                 }
@@ -279,6 +283,8 @@ int oracle_moe_forward(int T, int H, int I, int E, int K, float alpha, float lim
                 gate_up[i] = oracle_swiglu(gate[i], up[i], alpha, limit);
             if (round_mode == 1)
                 oracle_round_bf16_array(gate_up, I);
+            if (h_out)
+                memcpy(h_out + ((size_t)tok * K + k_pos) * I, gate_up, sizeof(float) * (size_t)I);
             oracle_matmul(tb2, gate_up, w2[e], I, H);
             for (int i = 0; i < H; i++)
                 tb2[i] += b2[e][i];

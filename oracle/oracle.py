@@ -193,9 +193,10 @@ def route(x_f32, w_router_f32, b_router, top_k, round_mode=1):
 
 
 def moe_forward(x_f32, w_router_f32, b_router, experts: ExpertCache, top_k=4, alpha=1.702,
-                limit=7.0, round_mode=1, impl="port"):
+                limit=7.0, round_mode=1, impl="port", want_h=False):
     """The MoE block for T tokens (src/run.cpp:628-707).  Returns a dict with
-    ``router_score`` [T,E], ``topk_i`` [T,K], ``topk_v`` [T,K], ``e_agg`` [T,H]."""
+    ``router_score`` [T,E], ``topk_i`` [T,K], ``topk_v`` [T,K], ``e_agg`` [T,H] and,
+    with ``want_h`` (port only), ``h`` [T,K,I], the input of MLP2 per selected expert."""
     x = np.ascontiguousarray(x_f32, dtype=np.float32)
     wr = np.ascontiguousarray(w_router_f32, dtype=np.float32)
     br = np.ascontiguousarray(b_router, dtype=np.float32)
@@ -217,6 +218,7 @@ def moe_forward(x_f32, w_router_f32, b_router, experts: ExpertCache, top_k=4, al
     topk_i = np.empty((T, top_k), dtype=np.int32)
     topk_v = np.empty((T, top_k), dtype=np.float32)
     e_agg = np.empty((T, H), dtype=np.float32)
+    h = np.empty((T, top_k, I), dtype=np.float32) if (want_h and impl == "port") else None
     if impl == "reference":
         if abs(alpha - 1.702) > 1e-9:
             raise ValueError("the reference hard-codes alpha = 1.702 (src/run.cpp:673)")
@@ -229,10 +231,14 @@ def moe_forward(x_f32, w_router_f32, b_router, experts: ExpertCache, top_k=4, al
                                             ctypes.c_float(limit), round_mode, _p(x, _f32p),
                                             _p(wr, _f32p), _p(br, _f32p), w1p, b1p, w2p, b2p,
                                             _p(scores, _f32p), _p(topk_i, _i32p),
-                                            _p(topk_v, _f32p), _p(e_agg, _f32p))
+                                            _p(topk_v, _f32p), _p(e_agg, _f32p),
+                                            _p(h, _f32p) if h is not None else None)
     if st != 0:
         raise RuntimeError(f"oracle: expert {-st - 1} selected but not provided")
-    return {"router_score": scores, "topk_i": topk_i, "topk_v": topk_v, "e_agg": e_agg}
+    res = {"router_score": scores, "topk_i": topk_i, "topk_v": topk_v, "e_agg": e_agg}
+    if h is not None:
+        res["h"] = h
+    return res
 
 
 def expert_rows(x_f32, w1, b1, w2, b2, alpha=1.702, limit=7.0, round_mode=1):

@@ -1,6 +1,20 @@
 """Shared helpers of the GPU parity tests: run the CUDA path through the C ABI
 and the CPU oracle on the same seeded inputs and compare under the stated
-tolerances."""
+tolerances.
+
+Output rule.  rel-L2 <= 2e-3 and max-abs <= 2e-2 against the bf16-weight /
+fp32-accumulate numerics (oracle round_mode 1).  The intermediate h (SwiGLU
+output, |h| up to 56) is rounded to bf16 before the down projection; any two
+correct fp32 evaluations of the gate/up GEMM differ in the last bits, so about
+one h element in 10^4 lands on the other side of a bf16 rounding boundary, and
+one such flip of a large h moves an output element by up to
+ulp(h) * max|W2| * routing weight = 0.25 * 0.375 * w -- above 2e-2 by itself.
+The max-abs gate is therefore applied to the output error that is NOT explained
+by identified one-ulp flips of h: the test reads the GPU's h, requires every
+difference from the oracle's h to be a single bf16 ulp and rarer than 1e-3,
+subtracts their exact effect (w * dh . W2^T) and requires the remainder to be
+within 2e-2.  The raw max-abs is reported alongside.
+"""
 import numpy as np
 import torch
 
@@ -8,20 +22,27 @@ import gpt_oss_amd_b200 as pkg
 from gpt_oss_amd_b200 import synth
 from oracle import oracle
 
-#: tolerances of the output comparison against the bf16-weight / fp32-accumulate
-#: numerics (oracle round_mode 1)
 REL_L2_TOL = 2e-3
 MAX_ABS_TOL = 2e-2
 TIE_EPS = 1e-6
+FLIP_RATE_TOL = 1e-3
 
 
-def oracle_case(lw, x_bits, round_mode=1, impl="port"):
+def expert_cache(lw):
+    return oracle.ExpertCache(lw.blocks1, lw.scales1, lw.bias1, lw.blocks2, lw.scales2, lw.bias2,
+                              first_expert=lw.first_expert)
+
+
+def oracle_case(lw, x_bits, round_mode=1, impl="port", cache=None):
     shape = lw.shape
     x = synth.bf16_bits_to_f32(x_bits)
     wr = synth.bf16_bits_to_f32(lw.w_router)
-    cache = oracle.ExpertCache(lw.blocks1, lw.scales1, lw.bias1, lw.blocks2, lw.scales2, lw.bias2)
-    return oracle.moe_forward(x, wr, lw.b_router, cache, top_k=shape.top_k, alpha=shape.alpha,
-                              limit=shape.limit, round_mode=round_mode, impl=impl)
+    cache = cache or expert_cache(lw)
+    ref = oracle.moe_forward(x, wr, lw.b_router, cache, top_k=shape.top_k, alpha=shape.alpha,
+                             limit=shape.limit, round_mode=round_mode, impl=impl,
+                             want_h=(impl == "port"))
+    ref["cache"] = cache
+    return ref
 
 
 def tie_mask(router_score, top_k):
@@ -33,21 +54,45 @@ def tie_mask(router_score, top_k):
     return (gaps < TIE_EPS).any(axis=1)
 
 
-def compare(out_gpu, topk_i_gpu, topk_w_gpu, ref, top_k, label=""):
-    """Asserts the parity rules; returns the measured figures."""
+def compare(res, ref, top_k, label=""):
+    """Asserts the parity rules (module docstring); returns the measured figures.
+    `res`: dict from run_gpu (out, topk_i, topk_w, optionally h_bits);
+    `ref`: dict from oracle_case."""
     ties = tie_mask(ref["router_score"], top_k)
     ok = ~ties
-    mism = (topk_i_gpu[ok] != ref["topk_i"][ok]).any(axis=1).sum()
+    mism = (res["topk_i"][ok] != ref["topk_i"][ok]).any(axis=1).sum()
     assert mism == 0, f"{label}: {mism} tokens with different expert indices (ties excluded: {ties.sum()})"
-    if topk_w_gpu is not None:
-        assert np.abs(topk_w_gpu[ok] - ref["topk_v"][ok]).max() < 1e-5, label
-    a, b = out_gpu[ok].astype(np.float64), ref["e_agg"][ok].astype(np.float64)
-    rel = np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
-    mx = np.abs(a - b).max() if a.size else 0.0
+    assert np.abs(res["topk_w"][ok] - ref["topk_v"][ok]).max(initial=0.0) < 1e-5, label
+    a, b = res["out"][ok].astype(np.float64), ref["e_agg"][ok].astype(np.float64)
     assert np.isfinite(a).all(), label
+    err = a - b
+    rel = np.linalg.norm(err) / max(np.linalg.norm(b), 1e-30)
+    raw = np.abs(err).max(initial=0.0)
+    m = {"rel_l2": float(rel), "max_abs_raw": float(raw), "max_abs": float(raw), "ties": int(ties.sum()),
+         "h_flips": 0, "h_elements": 0}
     assert rel <= REL_L2_TOL, f"{label}: rel-L2 {rel:.3e}"
-    assert mx <= MAX_ABS_TOL, f"{label}: max-abs {mx:.3e}"
-    return {"rel_l2": rel, "max_abs": mx, "ties": int(ties.sum())}
+    if "h_bits" in res and "h" in ref:
+        h_gpu = synth.bf16_bits_to_f32(res["h_bits"])[ok].astype(np.float64)
+        h_ref = ref["h"][ok].astype(np.float64)
+        dh = h_gpu - h_ref
+        flips = dh != 0
+        m["h_flips"], m["h_elements"] = int(flips.sum()), int(dh.size)
+        if flips.any():
+            big = np.maximum(np.abs(h_gpu), np.abs(h_ref))
+            assert (np.abs(dh[flips]) <= big[flips] * 2.0 ** -7 * 1.0001).all(), \
+                f"{label}: an intermediate differs by more than one bf16 ulp"
+            assert flips.mean() <= FLIP_RATE_TOL, f"{label}: flip rate {flips.mean():.2e}"
+            explained = np.zeros_like(err)
+            tok_idx = np.nonzero(ok)[0]
+            w = ref["topk_v"][ok].astype(np.float64)
+            for ti, k in zip(*np.nonzero(flips.any(axis=2))):
+                e = int(ref["topk_i"][tok_idx[ti], k])
+                w2 = ref["cache"].w2(e).astype(np.float64)  # [H, I]
+                explained[ti] += w[ti, k] * (w2 @ dh[ti, k])
+            m["max_abs"] = float(np.abs(err - explained).max(initial=0.0))
+    assert m["max_abs"] <= MAX_ABS_TOL, \
+        f"{label}: max-abs {m['max_abs']:.3e} (raw {raw:.3e}, {m['h_flips']} h flips)"
+    return m
 
 
 def run_gpu(shape, lw, x_bits, gemm_impl, dtype="bf16", max_tokens=None, accumulate_into=None):
@@ -60,16 +105,15 @@ def run_gpu(shape, lw, x_bits, gemm_impl, dtype="bf16", max_tokens=None, accumul
         if accumulate_into is not None:
             out = torch.from_numpy(accumulate_into.copy()).cuda()
             eng.forward(0, t, out=out, accumulate=True)
-            sc = ti = tw = None
-            out2, sc, ti, tw = eng.forward(0, t, side=True)
+            _, sc, ti, tw = eng.forward(0, t, side=True)
         else:
             out, sc, ti, tw = eng.forward(0, t, side=True)
+        h_bits = eng.last_intermediate(T)
         torch.cuda.synchronize()
         status = eng.device_status()
         assert status == 0, f"device status word 0x{status:x}"
-        res = {"out": out.cpu().numpy(), "score": sc.cpu().numpy(), "topk_i": ti.cpu().numpy(),
-               "topk_w": tw.cpu().numpy(), "launches": eng.last_launch_count(),
-               "counts": eng.last_expert_counts()}
-        return res
+        return {"out": out.cpu().numpy(), "score": sc.cpu().numpy(), "topk_i": ti.cpu().numpy(),
+                "topk_w": tw.cpu().numpy(), "h_bits": h_bits.cpu().numpy().view(np.uint16),
+                "launches": eng.last_launch_count(), "counts": eng.last_expert_counts()}
     finally:
         eng.close()
