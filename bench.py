@@ -139,8 +139,8 @@ def cpu_reference_run(wl, shape, steps, warmup, sample_tokens, seed=0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="prefill120b", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "mma_sync"])
     ap.add_argument("--cpu-sample", type=int, default=16, help="tokens in the CPU baseline sample")
@@ -237,11 +237,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(warmup):
-        step()
-    barrier()
-    launches_per_step = eng.last_launch_count() * wl["L"]
-
+    # clocks are sampled from the first warm-up step to the end of the timed steps
     sampler = None
     if rank == 0:
         uuid = None
@@ -252,8 +248,12 @@ def main():
         sampler = ClockSampler(uuid)
         sampler.start()
 
-    n_prof = min(args.steps * wl["L"], 4096)
-    eng.profile(n_prof)
+    for _ in range(warmup):
+        step()
+    barrier()
+    launches_per_step = eng.last_launch_count() * wl["L"]
+
+    # timed region: exactly args.steps steps, nothing else on the stream
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record(stream)
@@ -262,6 +262,15 @@ def main():
     ev1.record(stream)
     barrier()
     ms_total = ev0.elapsed_time(ev1)
+
+    # the same steps once more with CUDA-event pairs around every stage (on the
+    # launching stream) for the per-kernel durations behind `roofline`
+    n_prof = min(args.steps * wl["L"], 4096)
+    eng.profile(n_prof)
+    for _ in range((n_prof + wl["L"] - 1) // wl["L"]):
+        step()
+    barrier()
+    clocks = sampler.stop() if sampler else None
     stage_ms = {}
     for c in range(n_prof):
         for k, v in eng.profile_read(c).items():
@@ -284,7 +293,6 @@ def main():
             eng.forward_host(layer, x_host, out_host)
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
-    clocks = sampler.stop() if sampler else None
 
     ms_step = ms_total / args.steps
     if dist is not None:

@@ -26,6 +26,7 @@ REL_L2_TOL = 2e-3
 MAX_ABS_TOL = 2e-2
 TIE_EPS = 1e-6
 FLIP_RATE_TOL = 1e-3
+H_ABS_TOL = 2.0 ** -12  # differences of h below this are accepted whatever their ulp count
 
 
 def expert_cache(lw):
@@ -78,8 +79,11 @@ def compare(res, ref, top_k, label=""):
         flips = dh != 0
         m["h_flips"], m["h_elements"] = int(flips.sum()), int(dh.size)
         if flips.any():
+            # one bf16 ulp at the element's magnitude; where (up + 1) or the gate is
+            # close to zero h itself is tiny and a 1e-6 change of the pre-activation
+            # spans several of its ulps, so small absolute differences pass as well
             big = np.maximum(np.abs(h_gpu), np.abs(h_ref))
-            assert (np.abs(dh[flips]) <= big[flips] * 2.0 ** -7 * 1.0001).all(), \
+            assert (np.abs(dh[flips]) <= np.maximum(big[flips] * 2.0 ** -7 * 1.0001, H_ABS_TOL)).all(), \
                 f"{label}: an intermediate differs by more than one bf16 ulp"
             assert flips.mean() <= FLIP_RATE_TOL, f"{label}: flip rate {flips.mean():.2e}"
             explained = np.zeros_like(err)
