@@ -299,10 +299,16 @@ def main():
         tt = torch.tensor([ms_step, e2e_s], dtype=torch.float64, device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms_step, e2e_s = float(tt[0]), float(tt[1])
+    # every rank releases its handle at the same point: destroying the library's
+    # NCCL communicator is collective
+    counts_dev_bytes = eng.device_bytes()
+    if dist is not None:
+        dist.barrier()
+    eng.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
         return
 
     value = tokens_per_step_job / (ms_step * 1e-3)
@@ -357,11 +363,8 @@ def main():
         "stage_ms": {k: statistics.mean(v) for k, v in stage_ms.items()},
         "clocks": clocks,
     }
+    line["device_bytes_per_gpu"] = counts_dev_bytes
     print(json.dumps(line))
-    eng.close()
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

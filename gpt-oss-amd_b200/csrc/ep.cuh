@@ -42,9 +42,10 @@ struct State {
     std::vector<int> send_cnt, send_off, recv_cnt, recv_off;
 };
 
-typedef std::function<int(const uint16_t* xin, int rows_upper, const int* g_off, const int* g_cnt,
-                          const int* g_tile_start, float* yout, const int* row_dst)>
+typedef std::function<int(const uint16_t* xin, int rows_upper, int bn, const int* g_off,
+                          const int* g_cnt, const int* g_tile_start, float* yout, const int* row_dst)>
     GemmLauncher;
+typedef std::function<int(int rows)> PickBn;  // GEMM n-tile width for a call with `rows` local rows
 typedef std::function<void(int stage, bool begin)> StageMark;
 
 // Pure host arithmetic (also exported through the C ABI for tests): from the
@@ -240,8 +241,8 @@ inline int init(State& s, const char id_bytes[128], int G, int rank, std::string
 // cnt: this rank's per-(global)-expert row counts; xs: its rows sorted by
 // expert.  On return *y_out points at the fp32 result rows in the same order
 // as xs.
-inline int exchange_and_compute(State& s, const moe_b200_config& c, int n_local, int first, int bn,
-                                int T, const int* cnt, const uint16_t* xs, const GemmLauncher& gemms,
+inline int exchange_and_compute(State& s, const moe_b200_config& c, int n_local, int first,
+                                const PickBn& pick_bn, int T, const int* cnt, const uint16_t* xs, const GemmLauncher& gemms,
                                 const StageMark& mark, const float** y_out, cudaStream_t st,
                                 int* launches, std::string& err) {
     (void)T;
@@ -254,6 +255,7 @@ inline int exchange_and_compute(State& s, const moe_b200_config& c, int n_local,
     plan_exchange(E, G, rank, s.h_cnt_all, s.send_cnt.data(), s.send_off.data(), s.recv_cnt.data(),
                   s.recv_off.data());
     const int rows = s.recv_off[G - 1] + s.recv_cnt[G - 1];
+    const int bn = pick_bn(rows);
     EP_CUDA(cudaMemcpyAsync(s.recv_off_dev, s.recv_off.data(), (size_t)G * sizeof(int),
                             cudaMemcpyHostToDevice, st));
 
@@ -284,7 +286,7 @@ inline int exchange_and_compute(State& s, const moe_b200_config& c, int n_local,
     }
     mark(MOE_B200_STAGE_REGROUP, false);
     if (rows > 0) {
-        int gst = gemms(s.xgrp, rows, s.g_off, s.g_cnt, s.g_tile_start, s.ysend, s.gather_src);
+        int gst = gemms(s.xgrp, rows, bn, s.g_off, s.g_cnt, s.g_tile_start, s.ysend, s.gather_src);
         if (gst)
             return gst;
     }

@@ -11,14 +11,23 @@
 //
 // Orientation: D[128 weight rows, N token rows] = W_tile . X_tile^T, i.e. the
 // weight tile is the UMMA A operand (M = 128 TMEM lanes) and the token rows are
-// the B operand (N = 16..256 columns), so a ragged expert only narrows N.
+// the B operand (N = 16..BN columns), so a ragged expert only narrows N.
 //
-// Warp roles (448 threads):
-//   warp 0      producer: one bulk copy of the packed-MXFP4 chunk and one TMA
-//               tile of activations per stage
-//   warp 1      allocates tensor memory, issues tcgen05.mma, commits
-//   warps 2-9   decode packed MXFP4 -> bf16 into the 128B-swizzled A stage
-//   warps 10-13 epilogue: tcgen05.ld, bias, SwiGLU / store
+// Three rings of shared-memory slots, each with its own depth, so that the
+// HBM latency of the packed weights and the MXFP4 decode stay off the MMA's
+// critical path:
+//   W ring  packed MXFP4 chunks (4352 B)        bulk copy  -> decode warps
+//   A ring  decoded bf16 weight tiles (16 KB)   decode     -> tcgen05.mma
+//   B ring  activation tiles (BN x 128 B)       TMA        -> tcgen05.mma
+// The kernel is instantiated for BN = 64, 128 and 256 token rows per tile; a
+// smaller BN buys deeper B and W rings (decode-shaped batches are bound by
+// weight streaming, prefill-shaped ones by the tensor pipe).
+//
+// Warp roles (480 threads):
+//   warp 0       W producer        warp 1   B producer (TMA)
+//   warp 2       allocates tensor memory, issues tcgen05.mma, commits
+//   warps 3-10   decode packed MXFP4 -> bf16 into the 128B-swizzled A slot
+//   warps 11-14  epilogue: tcgen05.ld, bias, SwiGLU / store
 //
 // Every mbarrier wait is bounded in time; a wait that runs out records a code
 // in the handle's status word, raises a CTA-wide abort flag and all roles fall
@@ -27,23 +36,44 @@
 #include <cuda.h>
 
 #include "common.cuh"
-#include "gemm_mma.cuh"  // swiglu(), find_expert()
+#include "gemm_mma.cuh"  // swiglu()
 
 namespace moe {
 namespace tc5 {
 
-constexpr int BN = 256;                 // widest token tile (TMEM columns per accumulator)
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = TILE_M * 128;        // 128 rows x 64 bf16, SW128
-constexpr int B_STAGE_BYTES = BN * 128;            // 256 rows x 64 bf16, SW128
-constexpr int W_STAGE_BYTES = CHUNK_BYTES;         // packed chunk
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + W_STAGE_BYTES;
-constexpr int N_BARRIERS = 4 * STAGES + 4;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + N_BARRIERS * 8 + 64 + 1024;  // + align slack
-constexpr int THREADS = 448;
-constexpr int DEQ_WARP0 = 2, DEQ_WARPS = 8;
-constexpr int EPI_WARP0 = 10;
+constexpr int A_SLOT_BYTES = TILE_M * 128;  // 128 rows x 64 bf16, SW128
+constexpr int W_SLOT_BYTES = CHUNK_BYTES;   // packed chunk
+constexpr int THREADS = 480;
+constexpr int MMA_WARP = 2;
+constexpr int DEQ_WARP0 = 3, DEQ_WARPS = 8;
+constexpr int EPI_WARP0 = 11;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+// Ring depths per tile width.
+template <int BN>
+struct Geo;
+template <>
+struct Geo<256> {
+    static constexpr int AS = 4, BS = 4, WS = 6;
+};
+template <>
+struct Geo<128> {
+    static constexpr int AS = 4, BS = 6, WS = 8;
+};
+template <>
+struct Geo<64> {
+    static constexpr int AS = 4, BS = 12, WS = 12;
+};
+
+template <int BN>
+__host__ __device__ constexpr int n_barriers() {
+    return 2 * (Geo<BN>::AS + Geo<BN>::BS + Geo<BN>::WS) + 4;
+}
+template <int BN>
+__host__ __device__ constexpr int smem_bytes() {
+    return Geo<BN>::AS * A_SLOT_BYTES + Geo<BN>::BS * BN * 128 + Geo<BN>::WS * W_SLOT_BYTES +
+           n_barriers<BN>() * 8 + 64 + 1024;  // + holder/flag + alignment slack
+}
 
 struct TensorMaps {
     CUtensorMap box[4];  // token-row boxes of 32, 64, 128, 256 rows x 64 columns
@@ -110,6 +140,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     report_status(status, code);
     *abort_flag = 1;
     return false;
+}
+
+// After an abort: give a copy that was already issued a bounded time to land
+// before the CTA exits.
+__device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
+    const unsigned long long t0 = global_timer_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (global_timer_ns() - t0 > 100000000ull)  // 0.1 s
+            break;
+    }
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -216,6 +256,7 @@ struct TileInfo {
     int e, mt, row0, valid_n, n_mma, box_idx, box_rows;
 };
 
+template <int BN>
 __device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const int* __restrict__ g_off,
                                                 const int* __restrict__ g_cnt,
                                                 const int* __restrict__ g_tile_start, int E) {
@@ -243,7 +284,15 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const int
     return ti;
 }
 
-template <int MODE>
+#define RING_ADVANCE(s, ph, depth) \
+    do {                           \
+        if (++(s) == (depth)) {    \
+            (s) = 0;               \
+            (ph) ^= 1u;            \
+        }                          \
+    } while (0)
+
+template <int MODE, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __restrict__ chunks,
                        size_t expert_stride, int k_stages, int m_tiles,
@@ -252,33 +301,45 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                        const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
                        int out_ld, int out_rows_valid, const int* __restrict__ row_dst, float alpha,
                        float limit, int* __restrict__ status) {
+    constexpr int AS = Geo<BN>::AS, BS = Geo<BN>::BS, WS = Geo<BN>::WS;
+    constexpr int B_SLOT_BYTES = BN * 128;
+    constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 columns
+
     extern __shared__ unsigned char smem_dyn[];
-    // stage buffers need 1024-byte alignment for the 128-byte swizzle
+    // slots need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    unsigned char* a_stage = smem;
-    unsigned char* b_stage = smem + STAGES * A_STAGE_BYTES;
-    unsigned char* w_stage = b_stage + STAGES * B_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(w_stage + STAGES * W_STAGE_BYTES);
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + N_BARRIERS);
+    unsigned char* a_ring = smem;
+    unsigned char* b_ring = a_ring + AS * A_SLOT_BYTES;
+    unsigned char* w_ring = b_ring + BS * B_SLOT_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(w_ring + WS * W_SLOT_BYTES);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + n_barriers<BN>());
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const uint32_t bar0 = smem_u32(bars);
-    auto bar_full_w = [&](int s) { return bar0 + 8u * (uint32_t)s; };
-    auto bar_full_b = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
-    auto bar_full_a = [&](int s) { return bar0 + 8u * (uint32_t)(2 * STAGES + s); };
-    auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(3 * STAGES + s); };
-    auto bar_tmem_full = [&](int b) { return bar0 + 8u * (uint32_t)(4 * STAGES + b); };
-    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(4 * STAGES + 2 + b); };
+    auto bar_w_full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto bar_w_empty = [&](int s) { return bar0 + 8u * (uint32_t)(WS + s); };
+    auto bar_a_full = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + s); };
+    auto bar_a_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + AS + s); };
+    auto bar_b_full = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * AS + s); };
+    auto bar_b_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * AS + BS + s); };
+    auto bar_tmem_full = [&](int b) { return bar0 + 8u * (uint32_t)(2 * (WS + AS + BS) + b); };
+    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * (WS + AS + BS) + 2 + b); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(bar_full_w(s), 1);
-            mbar_init(bar_full_b(s), 1);
-            mbar_init(bar_full_a(s), DEQ_WARPS * 32);
-            mbar_init(bar_empty(s), 1);
+        for (int s = 0; s < WS; s++) {
+            mbar_init(bar_w_full(s), 1);
+            mbar_init(bar_w_empty(s), DEQ_WARPS * 32);
+        }
+        for (int s = 0; s < AS; s++) {
+            mbar_init(bar_a_full(s), DEQ_WARPS * 32);
+            mbar_init(bar_a_empty(s), 1);
+        }
+        for (int s = 0; s < BS; s++) {
+            mbar_init(bar_b_full(s), 1);
+            mbar_init(bar_b_empty(s), 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tmem_full(b), 1);
@@ -287,8 +348,8 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1)
-        tmem_alloc(smem_u32(tmem_holder), 512);
+    if (warp == MMA_WARP)
+        tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -297,60 +358,74 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     const int total_tiles = g_tile_start[E] * m_tiles;
 
     if (warp == 0) {
-        // ------------------------------ producer ------------------------------
+        // ------------------------- packed-weight producer ----------------------
         if (lane == 0) {
-            int s = 0;
+            int s = 0, armed = 0;
             uint32_t ph = 0;
             bool ok = true;
-            int armed = 0;  // stages armed and not yet known complete (for the abort drain)
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileInfo ti = decode_tile(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
                 const uint8_t* wsrc = chunks + (size_t)ti.e * expert_stride +
                                       (size_t)ti.mt * k_stages * CHUNK_BYTES;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    ok = mbar_wait(bar_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                    ok = mbar_wait(bar_w_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
                     if (!ok)
                         break;
-                    mbar_expect_tx(bar_full_w(s), W_STAGE_BYTES);
-                    bulk_load(smem_u32(w_stage + s * W_STAGE_BYTES), wsrc + (size_t)ks * CHUNK_BYTES,
-                              W_STAGE_BYTES, bar_full_w(s));
-                    mbar_expect_tx(bar_full_b(s), (uint32_t)ti.box_rows * 128u);
-                    tma_load_2d(smem_u32(b_stage + s * B_STAGE_BYTES), &maps.box[ti.box_idx],
-                                bar_full_b(s), ks * KSTAGE, ti.row0);
-                    armed = min(armed + 1, STAGES);
-                    if (++s == STAGES) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
+                    mbar_expect_tx(bar_w_full(s), W_SLOT_BYTES);
+                    bulk_load(smem_u32(w_ring + s * W_SLOT_BYTES), wsrc + (size_t)ks * CHUNK_BYTES,
+                              W_SLOT_BYTES, bar_w_full(s));
+                    armed = min(armed + 1, WS);
+                    RING_ADVANCE(s, ph, WS);
                 }
             }
             if (!ok) {
-                // give the copies already issued a bounded time to land before the
-                // CTA exits: walk back over the last `armed` stages
-                int ss = s;
-                uint32_t pp = ph;
-                for (int i = 0; i < armed; i++) {
-                    if (--ss < 0) {
-                        ss = STAGES - 1;
-                        pp ^= 1u;
+                for (int i = 0; i < armed; i++) {  // walk back over the copies in flight
+                    if (--s < 0) {
+                        s = WS - 1;
+                        ph ^= 1u;
                     }
-                    unsigned long long t0 = global_timer_ns();
-                    while (!(mbar_try_wait(bar_full_w(ss), pp) && mbar_try_wait(bar_full_b(ss), pp))) {
-                        if (global_timer_ns() - t0 > 100000000ull)
-                            break;
-                    }
+                    drain_wait(bar_w_full(s), ph);
                 }
             }
         }
     } else if (warp == 1) {
+        // ------------------------- activation-tile producer --------------------
+        if (lane == 0) {
+            int s = 0, armed = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                for (int ks = 0; ks < k_stages; ks++) {
+                    ok = mbar_wait(bar_b_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                    if (!ok)
+                        break;
+                    mbar_expect_tx(bar_b_full(s), (uint32_t)ti.box_rows * 128u);
+                    tma_load_2d(smem_u32(b_ring + s * B_SLOT_BYTES), &maps.box[ti.box_idx],
+                                bar_b_full(s), ks * KSTAGE, ti.row0);
+                    armed = min(armed + 1, BS);
+                    RING_ADVANCE(s, ph, BS);
+                }
+            }
+            if (!ok) {
+                for (int i = 0; i < armed; i++) {
+                    if (--s < 0) {
+                        s = BS - 1;
+                        ph ^= 1u;
+                    }
+                    drain_wait(bar_b_full(s), ph);
+                }
+            }
+        }
+    } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ----------------------------
         if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
+            int sa = 0, sb = 0;
+            uint32_t pha = 0, phb = 0;
             bool ok = true;
             int it = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-                const TileInfo ti = decode_tile(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
                 const int ab = it & 1;
                 ok = mbar_wait(bar_tmem_empty(ab), (uint32_t)((it >> 1) & 1) ^ 1u, status,
                                DS_TIMEOUT_TMEM_EMPTY, abort_flag);
@@ -360,24 +435,24 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                 const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
                 const uint32_t idesc = make_idesc(ti.n_mma);
                 for (int ks = 0; ks < k_stages; ks++) {
-                    ok = mbar_wait(bar_full_a(s), ph, status, DS_TIMEOUT_FULL_A, abort_flag) &&
-                         mbar_wait(bar_full_b(s), ph, status, DS_TIMEOUT_FULL_B, abort_flag);
+                    ok = mbar_wait(bar_a_full(sa), pha, status, DS_TIMEOUT_FULL_A, abort_flag) &&
+                         mbar_wait(bar_b_full(sb), phb, status, DS_TIMEOUT_FULL_B, abort_flag);
                     if (!ok)
                         break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(a_stage + s * A_STAGE_BYTES);
-                    const uint32_t b_addr = smem_u32(b_stage + s * B_STAGE_BYTES);
+                    const uint32_t a_addr = smem_u32(a_ring + sa * A_SLOT_BYTES);
+                    const uint32_t b_addr = smem_u32(b_ring + sb * B_SLOT_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < KSTAGE / 16; kk++) {
                         umma_bf16(d_tmem, make_sw128_desc(a_addr + kk * 32),
                                   make_sw128_desc(b_addr + kk * 32), idesc,
                                   (uint32_t)((ks | kk) != 0));
                     }
-                    umma_commit(bar_empty(s));  // frees this stage when the MMAs have read it
-                    if (++s == STAGES) {
-                        s = 0;
-                        ph ^= 1u;
-                    }
+                    // both slots are free once these MMAs have read them
+                    umma_commit(bar_a_empty(sa));
+                    umma_commit(bar_b_empty(sb));
+                    RING_ADVANCE(sa, pha, AS);
+                    RING_ADVANCE(sb, phb, BS);
                 }
                 if (ok)
                     umma_commit(bar_tmem_full(ab));
@@ -388,33 +463,40 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
         const int u = threadIdx.x - DEQ_WARP0 * 32;  // 0..255
         const int r = u & (TILE_M - 1), b = u >> 7;
         const uint32_t a_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        int s = 0;
-        uint32_t ph = 0;
+        int sw = 0, sa = 0;
+        uint32_t phw = 0, pha = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             for (int ks = 0; ks < k_stages; ks++) {
-                ok = mbar_wait(bar_full_w(s), ph, status, DS_TIMEOUT_FULL_W, abort_flag);
+                ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok)
                     break;
-                const unsigned char* wst = w_stage + s * W_STAGE_BYTES;
+                const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
                 const uint4 q = *reinterpret_cast<const uint4*>(wst + b * PLANE_BYTES + r * 16);
                 const uint32_t mult = mxfp4_scale_mult(wst[2 * PLANE_BYTES + r * 2 + b]);
                 const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-                unsigned char* arow = a_stage + s * A_STAGE_BYTES + a_row_off;
+                uint32_t d[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    mxfp4_decode_word(w[j], mult, d[j]);
+                mbar_arrive(bar_w_empty(sw));  // the packed chunk is in registers now
+                RING_ADVANCE(sw, phw, WS);
+
+                ok = mbar_wait(bar_a_empty(sa), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                unsigned char* arow = a_ring + sa * A_SLOT_BYTES + a_row_off;
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    uint32_t d[4];
-                    mxfp4_decode_word(w[j], mult, d);
                     const int chunk = (4 * b + j) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(arow + chunk * 16) = make_uint4(d[0], d[1], d[2], d[3]);
+                    *reinterpret_cast<uint4*>(arow + chunk * 16) =
+                        make_uint4(d[j][0], d[j][1], d[j][2], d[j][3]);
                 }
                 fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-                mbar_arrive(bar_full_a(s));
-                if (++s == STAGES) {
-                    s = 0;
-                    ph ^= 1u;
-                }
+                mbar_arrive(bar_a_full(sa));
+                RING_ADVANCE(sa, pha, AS);
             }
         }
     } else {
@@ -424,7 +506,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
         bool ok = true;
         int it = 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-            const TileInfo ti = decode_tile(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+            const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
             const int ab = it & 1;
             ok = mbar_wait(bar_tmem_full(ab), (uint32_t)((it >> 1) & 1), status,
                            DS_TIMEOUT_TMEM_FULL, abort_flag);
@@ -483,9 +565,9 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     // common exit: every role comes here, finished or aborted
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 

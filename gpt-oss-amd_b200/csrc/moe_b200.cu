@@ -42,7 +42,6 @@ struct moe_b200_handle_s {
     int first_expert = 0, n_local = 0;
     int m_tiles1 = 0, m_tiles2 = 0, ks1 = 0, ks2 = 0;
     size_t stride1 = 0, stride2 = 0;  // bytes per expert
-    int bn = 0;                       // token rows per GEMM n-tile
     int n_sms = 0;
     int rows_cap = 0;                 // rows the grouped buffers can hold
     int nblk_cap = 0;
@@ -75,7 +74,7 @@ struct moe_b200_handle_s {
     uint8_t* stage_scales = nullptr;
 
     tc5::TensorMaps maps_x{}, maps_h{};  // TMA maps over the GEMM inputs
-    bool tc5_ready = false;
+    int smem_attr_done = 0;  // bit set: shared-memory opt-in of a kernel family done on this device
 
     ep::State ep;
 
@@ -182,11 +181,10 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
                              const LayerWeights& lw, float* score_out, int nblk, cudaStream_t st) {
     if (route_block_tokens(T, h->cfg.hidden_dim) == RBS) {
         const size_t smem = route_small_smem_bytes(h->cfg.hidden_dim);
-        static size_t attr_smem = 0;
-        if (smem > attr_smem) {
+        if (!(h->smem_attr_done & 8)) {
             CU_TRY(h, cudaFuncSetAttribute(route_small_kernel<NT>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_smem = smem;
+            h->smem_attr_done |= 8;
         }
         route_small_kernel<NT><<<nblk, RBS * 32, smem, st>>>(
             t, t_dtype == MOE_B200_DTYPE_F32, T, h->cfg.hidden_dim, lw.w_router, lw.b_router,
@@ -194,12 +192,11 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
         return MOE_B200_OK;
     }
     const size_t smem = route_smem_bytes<NT>();
-    static bool attr_done = false;
-    if (!attr_done && smem > 48 * 1024) {
+    if (!(h->smem_attr_done & 16) && smem > 48 * 1024) {
         CU_TRY(h, cudaFuncSetAttribute(route_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     }
-    attr_done = true;
+    h->smem_attr_done |= 16;
     route_kernel<NT><<<nblk, RTHREADS, smem, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T,
                                                    h->cfg.hidden_dim, lw.w_router, lw.b_router,
                                                    h->cfg.n_experts, h->cfg.experts_per_token,
@@ -207,9 +204,39 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
     return MOE_B200_OK;
 }
 
-// The two grouped GEMMs over `g_*` tables describing rows grouped by local expert.
+template <int BN>
+moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
+                           const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
+                           const int* row_dst, cudaStream_t st) {
+    const moe_b200_config& c = h->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+    constexpr int smem = tc5::smem_bytes<BN>();
+    constexpr int bit = BN == 64 ? 1 : BN == 128 ? 2 : 4;
+    if (!(h->smem_attr_done & bit)) {  // per handle: the attribute is per device
+        CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<0, BN>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<1, BN>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        h->smem_attr_done |= bit;
+    }
+    prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
+    tc5::expert_gemm_tc5_kernel<0, BN><<<h->n_sms, tc5::THREADS, smem, st>>>(
+        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
+        EL, h->hbuf, I, I, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+    prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
+    tc5::expert_gemm_tc5_kernel<1, BN><<<h->n_sms, tc5::THREADS, smem, st>>>(
+        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
+        EL, yout, H, H, row_dst, c.swiglu_alpha, c.swiglu_limit, h->status);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    h->last_launches += 2;
+    return MOE_B200_OK;
+}
+
+// The two grouped GEMMs over `g_*` tables describing rows grouped by local
+// expert; `bn` is the n-tile width the tables were built for.
 moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const uint16_t* xin,
-                             const tc5::TensorMaps& maps_x, int rows_upper, const int* g_off,
+                             const tc5::TensorMaps& maps_x, int rows_upper, int bn, const int* g_off,
                              const int* g_cnt, const int* g_tile_start, float* yout,
                              const int* row_dst, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
@@ -227,29 +254,26 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
                                                       I, g_off, g_cnt, g_tile_start, EL, yout, H, H,
                                                       row_dst, c.swiglu_alpha, c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    } else if (bn == 64) {
+        return launch_tc5<64>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, st);
+    } else if (bn == 128) {
+        return launch_tc5<128>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, st);
     } else {
-        if (!h->tc5_ready) {
-            CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<0>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           tc5::SMEM_BYTES));
-            CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<1>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           tc5::SMEM_BYTES));
-            h->tc5_ready = true;
-        }
-        prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
-        tc5::expert_gemm_tc5_kernel<0><<<h->n_sms, tc5::THREADS, tc5::SMEM_BYTES, st>>>(
-            maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt,
-            g_tile_start, EL, h->hbuf, I, I, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
-        prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
-        prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
-        tc5::expert_gemm_tc5_kernel<1><<<h->n_sms, tc5::THREADS, tc5::SMEM_BYTES, st>>>(
-            h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt,
-            g_tile_start, EL, yout, H, H, row_dst, c.swiglu_alpha, c.swiglu_limit, h->status);
-        prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+        return launch_tc5<256>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, st);
     }
     h->last_launches += 2;
     return MOE_B200_OK;
+}
+
+// Token rows per GEMM n-tile for a call that has `rows` rows spread over the
+// local experts: a narrow tile (deeper weight and activation rings) when the
+// experts see few rows each and the call is bound by weight streaming, the
+// widest tile otherwise.  Any choice is correct for any distribution of rows.
+int pick_bn(moe_b200_handle h, int rows) {
+    if (h->cfg.gemm_impl == MOE_B200_GEMM_MMA_SYNC)
+        return V0_BN;
+    const int per_expert = rows / (h->n_local > 0 ? h->n_local : 1);
+    return per_expert <= 48 ? 64 : per_expert <= 96 ? 128 : 256;
 }
 
 }  // namespace
@@ -324,7 +348,6 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
     h->ks2 = I / KSTAGE;
     h->stride1 = (size_t)h->m_tiles1 * h->ks1 * CHUNK_BYTES;
     h->stride2 = (size_t)h->m_tiles2 * h->ks2 * CHUNK_BYTES;
-    h->bn = (c.gemm_impl == MOE_B200_GEMM_MMA_SYNC) ? V0_BN : tc5::BN;
     h->rows_cap = c.max_tokens * K * c.ep_size;
     {
         const int small = c.max_tokens < ROUTE_SMALL_MAX_TOKENS ? c.max_tokens : ROUTE_SMALL_MAX_TOKENS;
@@ -513,6 +536,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     const int T = n_tokens, H = c.hidden_dim, E = c.n_experts, K = c.experts_per_token;
     const int rb = route_block_tokens(T, H);
     const int nblk = ceil_div(T, rb);
+    const int bn_local = pick_bn(h, T * K);  // ep_size == 1: the GEMMs run on this rank's own rows
     h->last_launches = 0;
     h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
 
@@ -535,7 +559,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     // plan + permute also run for T == 0 on an expert-parallel rank (nblk == 0
     // gives all-zero counts), so that the collective below always has its inputs
     prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
-    plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, h->bn, h->cnt, h->off, h->tile_start,
+    plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off, h->tile_start,
                                   h->blk_base);
     prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
     h->last_launches++;
@@ -551,21 +575,22 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     const float* y_for_combine = h->ybuf;
     if (c.ep_size == 1) {
         if (T > 0) {
-            st = launch_gemms(h, lw, h->xs, h->maps_x, T * K, h->off, h->cnt, h->tile_start, h->ybuf,
-                              nullptr, s);
+            st = launch_gemms(h, lw, h->xs, h->maps_x, T * K, bn_local, h->off, h->cnt, h->tile_start,
+                              h->ybuf, nullptr, s);
             if (st)
                 return st;
         }
     } else {
-        ep::GemmLauncher gl = [&](const uint16_t* xin, int rows_upper, const int* g_off,
+        ep::GemmLauncher gl = [&](const uint16_t* xin, int rows_upper, int bn, const int* g_off,
                                   const int* g_cnt, const int* g_tile_start, float* yout,
                                   const int* row_dst) -> int {
-            return (int)launch_gemms(h, lw, xin, h->maps_x, rows_upper, g_off, g_cnt, g_tile_start,
-                                     yout, row_dst, s);
+            return (int)launch_gemms(h, lw, xin, h->maps_x, rows_upper, bn, g_off, g_cnt,
+                                     g_tile_start, yout, row_dst, s);
         };
+        ep::PickBn pick = [&](int rows) { return pick_bn(h, rows); };
         int launches = 0;
         ep::StageMark mark = [&](int stage, bool begin) { prof_mark(h, stage, begin, s); };
-        st = (moe_b200_status)ep::exchange_and_compute(h->ep, c, h->n_local, h->first_expert, h->bn,
+        st = (moe_b200_status)ep::exchange_and_compute(h->ep, c, h->n_local, h->first_expert, pick,
                                                        T, h->cnt, h->xs, gl, mark, &y_for_combine, s,
                                                        &launches, h->err);
         h->last_launches += launches;
