@@ -13,21 +13,27 @@
 // weight tile is the UMMA A operand (M = 128 TMEM lanes) and the token rows are
 // the B operand (N = 16..BN columns), so a ragged expert only narrows N.
 //
-// Three rings of shared-memory slots, each with its own depth, so that the
-// HBM latency of the packed weights and the MXFP4 decode stay off the MMA's
-// critical path:
-//   W ring  packed MXFP4 chunks (4352 B)        bulk copy  -> decode warps
-//   A ring  decoded bf16 weight tiles (16 KB)   decode     -> tcgen05.mma
-//   B ring  activation tiles (BN x 128 B)       TMA        -> tcgen05.mma
-// The kernel is instantiated for BN = 64, 128 and 256 token rows per tile; a
-// smaller BN buys deeper B and W rings (decode-shaped batches are bound by
-// weight streaming, prefill-shaped ones by the tensor pipe).
+// Shared-memory rings:
+//   W ring   packed MXFP4 chunks (4352 B), deep: covers the HBM latency
+//            bulk copy -> decode warps
+//   AB ring  STAGES slots, each a decoded bf16 weight tile (16 KB, written by
+//            the decode warps) plus an activation tile (BN x 128 B, written by
+//            TMA); ONE `full` barrier per slot collects the decode warps'
+//            arrivals and the TMA transaction bytes, ONE `empty` barrier per
+//            slot is signalled by tcgen05.commit -- the MMA-issuing thread does
+//            one wait and one commit per pipeline step, which is what bounds
+//            the step rate.
+// The kernel is instantiated for BN = 64, 128 and 256 token rows per tile.
+// Narrow tiles split the K loop over NACC accumulators in tensor memory (summed
+// in the epilogue): back-to-back MMAs into one accumulator are a dependent
+// chain whose latency, not throughput, bounds small-N tiles.
 //
-// Warp roles (480 threads):
+// Warp roles (736 threads):
 //   warp 0       W producer        warp 1   B producer (TMA)
 //   warp 2       allocates tensor memory, issues tcgen05.mma, commits
-//   warps 3-10   decode packed MXFP4 -> bf16 into the 128B-swizzled A slot
-//   warps 11-14  epilogue: tcgen05.ld, bias, SwiGLU / store
+//   warps 3-18   decode packed MXFP4 -> bf16 into the 128B-swizzled A slot,
+//                four groups of four warps working on four pipeline steps at once
+//   warps 19-22  epilogue: tcgen05.ld, bias, SwiGLU / store
 //
 // Every mbarrier wait is bounded in time; a wait that runs out records a code
 // in the handle's status word, raises a CTA-wide abort flag and all roles fall
@@ -43,36 +49,38 @@ namespace tc5 {
 
 constexpr int A_SLOT_BYTES = TILE_M * 128;  // 128 rows x 64 bf16, SW128
 constexpr int W_SLOT_BYTES = CHUNK_BYTES;   // packed chunk
-constexpr int THREADS = 480;
+constexpr int STAGES = 4;                   // AB ring depth = number of decode groups
 constexpr int MMA_WARP = 2;
-constexpr int DEQ_WARP0 = 3, DEQ_WARPS = 8;
-constexpr int EPI_WARP0 = 11;
+constexpr int DEQ_WARP0 = 3, DEQ_GROUPS = STAGES, DEQ_WARPS = 4 * DEQ_GROUPS;
+constexpr int EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS;  // 19: warps 19..22 cover the four TMEM lane quarters
+constexpr int THREADS = (EPI_WARP0 + 4) * 32;     // 736
+constexpr int MAX_LOCAL_EXPERTS = 256;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
-// Ring depths per tile width.
+// W ring depth and number of K-split accumulators per tile width.
 template <int BN>
 struct Geo;
 template <>
 struct Geo<256> {
-    static constexpr int AS = 4, BS = 4, WS = 6;
+    static constexpr int WS = 6, NACC = 1;
 };
 template <>
 struct Geo<128> {
-    static constexpr int AS = 4, BS = 6, WS = 8;
+    static constexpr int WS = 12, NACC = 2;
 };
 template <>
 struct Geo<64> {
-    static constexpr int AS = 4, BS = 12, WS = 12;
+    static constexpr int WS = 16, NACC = 4;
 };
 
 template <int BN>
 __host__ __device__ constexpr int n_barriers() {
-    return 2 * (Geo<BN>::AS + Geo<BN>::BS + Geo<BN>::WS) + 4;
+    return 2 * Geo<BN>::WS + 2 * STAGES + 4;
 }
 template <int BN>
 __host__ __device__ constexpr int smem_bytes() {
-    return Geo<BN>::AS * A_SLOT_BYTES + Geo<BN>::BS * BN * 128 + Geo<BN>::WS * W_SLOT_BYTES +
-           n_barriers<BN>() * 8 + 64 + 1024;  // + holder/flag + alignment slack
+    return STAGES * (A_SLOT_BYTES + BN * 128) + Geo<BN>::WS * W_SLOT_BYTES + n_barriers<BN>() * 8 +
+           (MAX_LOCAL_EXPERTS + 1) * 3 * 4 + 64 + 1024;  // + tile tables + holder/flag + alignment slack
 }
 
 struct TensorMaps {
@@ -211,9 +219,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane
-// (taddr.lane + i), registers = columns.
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float v[32]) {
-    uint32_t r[32];
+// (taddr.lane + i), registers = columns.  No wait: pair with tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t r[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -225,10 +232,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float v[32]) {
           "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Sum over the NACC K-split accumulators (BN columns apart) of 32 columns.
+template <int NACC, int BN>
+__device__ __forceinline__ void tmem_ld_sum(uint32_t taddr, float v[32]) {
+    uint32_t r[32];
+    tmem_ld_32x32_issue(taddr, r);
+    tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 32; i++)
         v[i] = __uint_as_float(r[i]);
+#pragma unroll
+    for (int a = 1; a < NACC; a++) {
+        tmem_ld_32x32_issue(taddr + (uint32_t)(a * BN), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++)
+            v[i] += __uint_as_float(r[i]);
+    }
 }
 
 // Shared-memory matrix descriptor: K-major tile whose rows are 128 bytes
@@ -256,28 +281,35 @@ struct TileInfo {
     int e, mt, row0, valid_n, n_mma, box_idx, box_rows;
 };
 
+// The tile tables live in shared memory (copied once per CTA): every role
+// decodes every tile it touches, and a binary search over global memory costs
+// several L2 round trips.
+struct TileTables {
+    const int* off;         // [E + 1]
+    const int* cnt;         // [E]
+    const int* tile_start;  // [E + 1]
+};
+
 template <int BN>
-__device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const int* __restrict__ g_off,
-                                                const int* __restrict__ g_cnt,
-                                                const int* __restrict__ g_tile_start, int E) {
+__device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const TileTables& tt, int E) {
     // tiles ordered [expert][m_tile][n_tile]: the n-tiles that share a weight
     // chunk run on neighbouring CTAs at the same time and meet in L2
     int lo = 0, hi = E;
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
-        if (g_tile_start[mid] * m_tiles <= tile)
+        if (tt.tile_start[mid] * m_tiles <= tile)
             lo = mid;
         else
             hi = mid;
     }
     TileInfo ti;
     ti.e = lo;
-    const int ntl = g_tile_start[lo + 1] - g_tile_start[lo];
-    const int r = tile - g_tile_start[lo] * m_tiles;
+    const int ntl = tt.tile_start[lo + 1] - tt.tile_start[lo];
+    const int r = tile - tt.tile_start[lo] * m_tiles;
     ti.mt = r / ntl;
     const int n0 = (r - ti.mt * ntl) * BN;
-    ti.row0 = g_off[lo] + n0;
-    ti.valid_n = min(BN, g_cnt[lo] - n0);
+    ti.row0 = tt.off[lo] + n0;
+    ti.valid_n = min(BN, tt.cnt[lo] - n0);
     ti.n_mma = max(16, (ti.valid_n + 15) & ~15);
     ti.box_idx = ti.n_mma <= 32 ? 0 : ti.n_mma <= 64 ? 1 : ti.n_mma <= 128 ? 2 : 3;
     ti.box_rows = 32 << ti.box_idx;
@@ -301,52 +333,54 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                        const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
                        int out_ld, int out_rows_valid, const int* __restrict__ row_dst, float alpha,
                        float limit, int* __restrict__ status) {
-    constexpr int AS = Geo<BN>::AS, BS = Geo<BN>::BS, WS = Geo<BN>::WS;
+    constexpr int WS = Geo<BN>::WS, NACC = Geo<BN>::NACC;
     constexpr int B_SLOT_BYTES = BN * 128;
-    constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 columns
+    constexpr int ACC_COLS = NACC * BN;        // columns of one accumulator set
+    constexpr int TMEM_COLS = 2 * ACC_COLS;    // two sets (MMA of tile i+1 overlaps epilogue of tile i)
+    static_assert(TMEM_COLS == 512, "the accumulator sets fill tensor memory");
 
     extern __shared__ unsigned char smem_dyn[];
     // slots need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     unsigned char* a_ring = smem;
-    unsigned char* b_ring = a_ring + AS * A_SLOT_BYTES;
-    unsigned char* w_ring = b_ring + BS * B_SLOT_BYTES;
+    unsigned char* b_ring = a_ring + STAGES * A_SLOT_BYTES;
+    unsigned char* w_ring = b_ring + STAGES * B_SLOT_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(w_ring + WS * W_SLOT_BYTES);
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + n_barriers<BN>());
+    int* s_tables = reinterpret_cast<int*>(bars + n_barriers<BN>());
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(s_tables + 3 * (MAX_LOCAL_EXPERTS + 1));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const uint32_t bar0 = smem_u32(bars);
     auto bar_w_full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto bar_w_empty = [&](int s) { return bar0 + 8u * (uint32_t)(WS + s); };
-    auto bar_a_full = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + s); };
-    auto bar_a_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + AS + s); };
-    auto bar_b_full = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * AS + s); };
-    auto bar_b_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * AS + BS + s); };
-    auto bar_tmem_full = [&](int b) { return bar0 + 8u * (uint32_t)(2 * (WS + AS + BS) + b); };
-    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * (WS + AS + BS) + 2 + b); };
+    auto bar_full = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + STAGES + s); };
+    auto bar_tmem_full = [&](int b) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * STAGES + b); };
+    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * STAGES + 2 + b); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < WS; s++) {
             mbar_init(bar_w_full(s), 1);
-            mbar_init(bar_w_empty(s), DEQ_WARPS * 32);
+            mbar_init(bar_w_empty(s), 4);  // one elected arrival per warp of the decoding group
         }
-        for (int s = 0; s < AS; s++) {
-            mbar_init(bar_a_full(s), DEQ_WARPS * 32);
-            mbar_init(bar_a_empty(s), 1);
-        }
-        for (int s = 0; s < BS; s++) {
-            mbar_init(bar_b_full(s), 1);
-            mbar_init(bar_b_empty(s), 1);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full(s), 4 + 1);  // four decode warps + the TMA producer's expect_tx
+            mbar_init(bar_empty(s), 1);     // tcgen05.commit
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tmem_full(b), 1);
-            mbar_init(bar_tmem_empty(b), 128);
+            mbar_init(bar_tmem_empty(b), 4);  // one per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
+    }
+    for (int i = threadIdx.x; i <= E; i += THREADS) {
+        s_tables[i] = g_off[i];
+        s_tables[(MAX_LOCAL_EXPERTS + 1) + i] = (i < E) ? g_cnt[i] : 0;
+        s_tables[2 * (MAX_LOCAL_EXPERTS + 1) + i] = g_tile_start[i];
     }
     if (warp == MMA_WARP)
         tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
@@ -354,8 +388,12 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    TileTables tt;
+    tt.off = s_tables;
+    tt.cnt = s_tables + (MAX_LOCAL_EXPERTS + 1);
+    tt.tile_start = s_tables + 2 * (MAX_LOCAL_EXPERTS + 1);
 
-    const int total_tiles = g_tile_start[E] * m_tiles;
+    const int total_tiles = tt.tile_start[E] * m_tiles;
 
     if (warp == 0) {
         // ------------------------- packed-weight producer ----------------------
@@ -364,7 +402,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
                 const uint8_t* wsrc = chunks + (size_t)ti.e * expert_stride +
                                       (size_t)ti.mt * k_stages * CHUNK_BYTES;
                 for (int ks = 0; ks < k_stages; ks++) {
@@ -391,68 +429,61 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     } else if (warp == 1) {
         // ------------------------- activation-tile producer --------------------
         if (lane == 0) {
-            int s = 0, armed = 0;
+            int s = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
                 for (int ks = 0; ks < k_stages; ks++) {
-                    ok = mbar_wait(bar_b_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                    ok = mbar_wait(bar_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
                     if (!ok)
                         break;
-                    mbar_expect_tx(bar_b_full(s), (uint32_t)ti.box_rows * 128u);
+                    mbar_expect_tx(bar_full(s), (uint32_t)ti.box_rows * 128u);
                     tma_load_2d(smem_u32(b_ring + s * B_SLOT_BYTES), &maps.box[ti.box_idx],
-                                bar_b_full(s), ks * KSTAGE, ti.row0);
-                    armed = min(armed + 1, BS);
-                    RING_ADVANCE(s, ph, BS);
+                                bar_full(s), ks * KSTAGE, ti.row0);
+                    RING_ADVANCE(s, ph, STAGES);
                 }
             }
-            if (!ok) {
-                for (int i = 0; i < armed; i++) {
-                    if (--s < 0) {
-                        s = BS - 1;
-                        ph ^= 1u;
-                    }
-                    drain_wait(bar_b_full(s), ph);
-                }
-            }
+            // after an abort the copies in flight complete on `full` barriers whose other
+            // arrivals may never come; the common exit below gives them time to land
+            if (!ok)
+                drain_wait(bar_full(s), ph ^ 1u);
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ----------------------------
         if (lane == 0) {
-            int sa = 0, sb = 0;
-            uint32_t pha = 0, phb = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
             int it = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
                 const int ab = it & 1;
                 ok = mbar_wait(bar_tmem_empty(ab), (uint32_t)((it >> 1) & 1) ^ 1u, status,
                                DS_TIMEOUT_TMEM_EMPTY, abort_flag);
                 if (!ok)
                     break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * ACC_COLS);
                 const uint32_t idesc = make_idesc(ti.n_mma);
                 for (int ks = 0; ks < k_stages; ks++) {
-                    ok = mbar_wait(bar_a_full(sa), pha, status, DS_TIMEOUT_FULL_A, abort_flag) &&
-                         mbar_wait(bar_b_full(sb), phb, status, DS_TIMEOUT_FULL_B, abort_flag);
+                    ok = mbar_wait(bar_full(s), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
                     if (!ok)
                         break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(a_ring + sa * A_SLOT_BYTES);
-                    const uint32_t b_addr = smem_u32(b_ring + sb * B_SLOT_BYTES);
+                    const uint64_t a_desc = make_sw128_desc(smem_u32(a_ring + s * A_SLOT_BYTES));
+                    const uint64_t b_desc = make_sw128_desc(smem_u32(b_ring + s * B_SLOT_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < KSTAGE / 16; kk++) {
-                        umma_bf16(d_tmem, make_sw128_desc(a_addr + kk * 32),
-                                  make_sw128_desc(b_addr + kk * 32), idesc,
-                                  (uint32_t)((ks | kk) != 0));
+                        // K-split: MMA kk goes to accumulator kk % NACC; each accumulator's
+                        // first MMA of the tile overwrites
+                        const int acc = kk % NACC;
+                        const uint32_t first = (ks == 0 && kk < NACC) ? 0u : 1u;
+                        umma_bf16(d_tmem + (uint32_t)(acc * BN), a_desc + (uint64_t)(kk * 2),
+                                  b_desc + (uint64_t)(kk * 2), idesc, first);
                     }
-                    // both slots are free once these MMAs have read them
-                    umma_commit(bar_a_empty(sa));
-                    umma_commit(bar_b_empty(sb));
-                    RING_ADVANCE(sa, pha, AS);
-                    RING_ADVANCE(sb, phb, BS);
+                    umma_commit(bar_empty(s));  // frees the slot when these MMAs have read it
+                    RING_ADVANCE(s, ph, STAGES);
                 }
                 if (ok)
                     umma_commit(bar_tmem_full(ab));
@@ -460,44 +491,57 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
         }
     } else if (warp < EPI_WARP0) {
         // ------------------------------ MXFP4 decode --------------------------
-        const int u = threadIdx.x - DEQ_WARP0 * 32;  // 0..255
-        const int r = u & (TILE_M - 1), b = u >> 7;
+        // DEQ_GROUPS groups of 4 warps; group g decodes the pipeline steps
+        // g, g + DEQ_GROUPS, ... into AB slot g, so that several steps are in
+        // flight at once (one step is a chain of waits, loads and dependent ALU
+        // instructions, longer than the MMAs of a step).  A thread owns one weight
+        // row of the tile and decodes both of its 32-column blocks.
+        const int u = threadIdx.x - DEQ_WARP0 * 32;
+        const int g = u >> 7;            // group = AB slot
+        const int r = u & (TILE_M - 1);  // weight row inside the tile
         const uint32_t a_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        int sw = 0, sa = 0;
-        uint32_t phw = 0, pha = 0;
+        const int my_tiles = (int)blockIdx.x < total_tiles
+                                 ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        const int total_steps = my_tiles * k_stages;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            for (int ks = 0; ks < k_stages; ks++) {
-                ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok)
-                    break;
-                const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
-                const uint4 q = *reinterpret_cast<const uint4*>(wst + b * PLANE_BYTES + r * 16);
-                const uint32_t mult = mxfp4_scale_mult(wst[2 * PLANE_BYTES + r * 2 + b]);
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-                uint32_t d[4][4];
+        for (int i = g; ok && i < total_steps; i += DEQ_GROUPS) {
+            const int sw = i % WS;
+            const uint32_t phw = (uint32_t)(i / WS) & 1u, pha = (uint32_t)(i / STAGES) & 1u;
+            ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
+            const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
+            const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
+            const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
+            const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu), mult1 = mxfp4_scale_mult(sc >> 8);
+            const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            uint32_t d[8][4];
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    mxfp4_decode_word(w[j], mult, d[j]);
-                mbar_arrive(bar_w_empty(sw));  // the packed chunk is in registers now
-                RING_ADVANCE(sw, phw, WS);
+            for (int j = 0; j < 8; j++)
+                mxfp4_decode_word(w[j], j < 4 ? mult0 : mult1, d[j]);
+            // the packed chunk is in registers now.  One arrival per warp: hundreds
+            // of per-thread arrivals on one mbarrier serialise in shared memory
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(bar_w_empty(sw));
 
-                ok = mbar_wait(bar_a_empty(sa), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok)
-                    break;
-                unsigned char* arow = a_ring + sa * A_SLOT_BYTES + a_row_off;
+            ok = mbar_wait(bar_empty(g), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            unsigned char* arow = a_ring + g * A_SLOT_BYTES + a_row_off;
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int chunk = (4 * b + j) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(arow + chunk * 16) =
-                        make_uint4(d[j][0], d[j][1], d[j][2], d[j][3]);
-                }
-                fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-                mbar_arrive(bar_a_full(sa));
-                RING_ADVANCE(sa, pha, AS);
+            for (int j = 0; j < 8; j++) {
+                const int chunk = j ^ (r & 7);
+                *reinterpret_cast<uint4*>(arow + chunk * 16) =
+                    make_uint4(d[j][0], d[j][1], d[j][2], d[j][3]);
             }
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(bar_full(g));
         }
     } else {
         // ------------------------------ epilogue ------------------------------
@@ -506,7 +550,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
         bool ok = true;
         int it = 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-            const TileInfo ti = decode_tile<BN>(tile, m_tiles, g_off, g_cnt, g_tile_start, E);
+            const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
             const int ab = it & 1;
             ok = mbar_wait(bar_tmem_full(ab), (uint32_t)((it >> 1) & 1), status,
                            DS_TIMEOUT_TMEM_FULL, abort_flag);
@@ -516,7 +560,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             tc_fence_after();
             const float* be = bias + (size_t)ti.e * bias_stride;
             const int m = ti.mt * TILE_M + row;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * ACC_COLS);
             if (MODE == 0) {
                 uint16_t* h = static_cast<uint16_t*>(outp);
                 const float bm = be[m];  // 2I is a multiple of TILE_M: always in range
@@ -524,7 +568,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                 const bool odd = (lane & 1) != 0;
                 for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
                     float v[32];
-                    tmem_ld_32x32(t_addr + (uint32_t)c0, v);
+                    tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         // even lane = gate row, odd lane = the matching up row: the even
@@ -546,7 +590,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                 const float bm = m_ok ? be[m] : 0.f;
                 for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
                     float v[32];
-                    tmem_ld_32x32(t_addr + (uint32_t)c0, v);
+                    tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int col = c0 + j;
@@ -558,7 +602,9 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                 }
             }
             tc_fence_before();
-            mbar_arrive(bar_tmem_empty(ab));
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(bar_tmem_empty(ab));
         }
     }
 
