@@ -47,39 +47,54 @@
 namespace moe {
 namespace tc5 {
 
-constexpr int A_SLOT_BYTES = TILE_M * 128;  // 128 rows x 64 bf16, SW128
-constexpr int W_SLOT_BYTES = CHUNK_BYTES;   // packed chunk
-constexpr int STAGES = 4;                   // AB ring depth = number of decode groups
+constexpr int A_TILE_BYTES = TILE_M * 128;  // one decoded weight tile: 128 rows x 64 bf16, SW128
 constexpr int MMA_WARP = 2;
-constexpr int DEQ_WARP0 = 3, DEQ_GROUPS = STAGES, DEQ_WARPS = 4 * DEQ_GROUPS;
-constexpr int EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS;  // 19: warps 19..22 cover the four TMEM lane quarters
-constexpr int THREADS = (EPI_WARP0 + 4) * 32;     // 736
+constexpr int DEQ_WARP0 = 3;
 constexpr int MAX_LOCAL_EXPERTS = 256;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
-// W ring depth and number of K-split accumulators per tile width.
+// Geometry per tile width BN (token rows per work item):
+//   MT      weight tiles (of 128 rows) per work item.  The activation tile is
+//           what a CTA pulls through L2 at every step; feeding two weight tiles
+//           from it halves that traffic per FLOP, which is what bounds the
+//           prefill-shaped GEMM (L2 -> SM bandwidth, not the tensor pipe)
+//   G       decode groups (of four warps); group g decodes pipeline steps g, g+G, ...
+//   STAGES  depth of the AB ring     WS  depth of the packed-weight ring.  Both are
+//           multiples of G, so the successive fills of a slot are consumed by the same
+//           group in program order: an mbarrier parity wait cannot tell phase n from
+//           phase n-2, so a waiter must never run two phases ahead of a slot
+//   NACC    K-split accumulators per weight tile (narrow tiles: back-to-back
+//           MMAs into one accumulator are a dependent chain)
+//   SETS    accumulator sets in tensor memory (2 = the MMAs of the next work
+//           item overlap the epilogue of this one)
+// SETS * MT * NACC * BN = 512 columns in every case.
 template <int BN>
 struct Geo;
 template <>
 struct Geo<256> {
-    static constexpr int WS = 6, NACC = 1;
+    static constexpr int MT = 1, G = 4, STAGES = 4, WS = 4, NACC = 1, SETS = 2;
 };
 template <>
 struct Geo<128> {
-    static constexpr int WS = 12, NACC = 2;
+    static constexpr int MT = 1, G = 4, STAGES = 4, WS = 12, NACC = 2, SETS = 2;
 };
 template <>
 struct Geo<64> {
-    static constexpr int WS = 16, NACC = 4;
+    static constexpr int MT = 1, G = 4, STAGES = 4, WS = 16, NACC = 4, SETS = 2;
 };
 
 template <int BN>
+__host__ __device__ constexpr int n_threads() {
+    return (DEQ_WARP0 + 4 * Geo<BN>::G + 4 * Geo<BN>::MT) * 32;  // 608 or 736
+}
+template <int BN>
 __host__ __device__ constexpr int n_barriers() {
-    return 2 * Geo<BN>::WS + 2 * STAGES + 4;
+    return 2 * Geo<BN>::WS + 2 * Geo<BN>::STAGES + 2 * Geo<BN>::SETS;
 }
 template <int BN>
 __host__ __device__ constexpr int smem_bytes() {
-    return STAGES * (A_SLOT_BYTES + BN * 128) + Geo<BN>::WS * W_SLOT_BYTES + n_barriers<BN>() * 8 +
+    return Geo<BN>::STAGES * (Geo<BN>::MT * A_TILE_BYTES + BN * 128) +
+           Geo<BN>::WS * Geo<BN>::MT * CHUNK_BYTES + n_barriers<BN>() * 8 +
            (MAX_LOCAL_EXPERTS + 1) * 3 * 4 + 64 + 1024;  // + tile tables + holder/flag + alignment slack
 }
 
@@ -277,27 +292,30 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
            | ((uint32_t)(TILE_M >> 4) << 24);  // M / 16
 }
 
+
 struct TileInfo {
-    int e, mt, row0, valid_n, n_mma, box_idx, box_rows;
+    int e, mt0, n_mt, row0, valid_n, n_mma, box_idx, box_rows;
 };
 
 // The tile tables live in shared memory (copied once per CTA): every role
-// decodes every tile it touches, and a binary search over global memory costs
-// several L2 round trips.
+// decodes every work item it touches, and a binary search over global memory
+// costs several L2 round trips.
 struct TileTables {
     const int* off;         // [E + 1]
     const int* cnt;         // [E]
     const int* tile_start;  // [E + 1]
 };
 
+// Work items ordered [expert][m_item][n_tile]: the n-tiles that share weight
+// chunks run on neighbouring CTAs at the same time and meet in L2.  An m_item
+// is MT consecutive weight tiles (the last one of a matrix may hold fewer).
 template <int BN>
-__device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const TileTables& tt, int E) {
-    // tiles ordered [expert][m_tile][n_tile]: the n-tiles that share a weight
-    // chunk run on neighbouring CTAs at the same time and meet in L2
+__device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, int m_items,
+                                                const TileTables& tt, int E) {
     int lo = 0, hi = E;
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
-        if (tt.tile_start[mid] * m_tiles <= tile)
+        if (tt.tile_start[mid] * m_items <= tile)
             lo = mid;
         else
             hi = mid;
@@ -305,9 +323,11 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const Til
     TileInfo ti;
     ti.e = lo;
     const int ntl = tt.tile_start[lo + 1] - tt.tile_start[lo];
-    const int r = tile - tt.tile_start[lo] * m_tiles;
-    ti.mt = r / ntl;
-    const int n0 = (r - ti.mt * ntl) * BN;
+    const int r = tile - tt.tile_start[lo] * m_items;
+    const int mi = r / ntl;
+    ti.mt0 = mi * Geo<BN>::MT;
+    ti.n_mt = min(Geo<BN>::MT, m_tiles - ti.mt0);
+    const int n0 = (r - mi * ntl) * BN;
     ti.row0 = tt.off[lo] + n0;
     ti.valid_n = min(BN, tt.cnt[lo] - n0);
     ti.n_mma = max(16, (ti.valid_n + 15) & ~15);
@@ -325,7 +345,7 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const Til
     } while (0)
 
 template <int MODE, int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(n_threads<BN>(), 1)
 expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __restrict__ chunks,
                        size_t expert_stride, int k_stages, int m_tiles,
                        const float* __restrict__ bias, int bias_stride,
@@ -333,11 +353,20 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                        const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
                        int out_ld, int out_rows_valid, const int* __restrict__ row_dst, float alpha,
                        float limit, int* __restrict__ status) {
-    constexpr int WS = Geo<BN>::WS, NACC = Geo<BN>::NACC;
+    constexpr int MT = Geo<BN>::MT, STAGES = Geo<BN>::STAGES, WS = Geo<BN>::WS;
+    constexpr int NACC = Geo<BN>::NACC, SETS = Geo<BN>::SETS;
+    constexpr int THREADS = n_threads<BN>();
+    constexpr int A_SLOT_BYTES = MT * A_TILE_BYTES;
     constexpr int B_SLOT_BYTES = BN * 128;
-    constexpr int ACC_COLS = NACC * BN;        // columns of one accumulator set
-    constexpr int TMEM_COLS = 2 * ACC_COLS;    // two sets (MMA of tile i+1 overlaps epilogue of tile i)
+    constexpr int W_SLOT_BYTES = MT * CHUNK_BYTES;
+    constexpr int SET_COLS = MT * NACC * BN;  // columns of one accumulator set
+    constexpr int TMEM_COLS = SETS * SET_COLS;
+    constexpr int EPI_WARPS = 4 * MT;
+    constexpr int DEQ_GROUPS = Geo<BN>::G;
+    constexpr int EPI_WARP0 = DEQ_WARP0 + 4 * DEQ_GROUPS;  // any four consecutive warps cover the four TMEM lane quarters
     static_assert(TMEM_COLS == 512, "the accumulator sets fill tensor memory");
+    static_assert(STAGES % DEQ_GROUPS == 0 && WS % DEQ_GROUPS == 0,
+                  "a slot's successive fills must belong to one decode group");
 
     extern __shared__ unsigned char smem_dyn[];
     // slots need 1024-byte alignment for the 128-byte swizzle
@@ -357,7 +386,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     auto bar_full = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (uint32_t)(2 * WS + STAGES + s); };
     auto bar_tmem_full = [&](int b) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * STAGES + b); };
-    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * STAGES + 2 + b); };
+    auto bar_tmem_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * WS + 2 * STAGES + SETS + b); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -370,9 +399,9 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             mbar_init(bar_full(s), 4 + 1);  // four decode warps + the TMA producer's expect_tx
             mbar_init(bar_empty(s), 1);     // tcgen05.commit
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < SETS; b++) {
             mbar_init(bar_tmem_full(b), 1);
-            mbar_init(bar_tmem_empty(b), 4);  // one per epilogue warp
+            mbar_init(bar_tmem_empty(b), EPI_WARPS);  // one per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -393,7 +422,8 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     tt.cnt = s_tables + (MAX_LOCAL_EXPERTS + 1);
     tt.tile_start = s_tables + 2 * (MAX_LOCAL_EXPERTS + 1);
 
-    const int total_tiles = tt.tile_start[E] * m_tiles;
+    const int m_items = (m_tiles + MT - 1) / MT;
+    const int total_tiles = tt.tile_start[E] * m_items;
 
     if (warp == 0) {
         // ------------------------- packed-weight producer ----------------------
@@ -402,16 +432,18 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, m_items, tt, E);
                 const uint8_t* wsrc = chunks + (size_t)ti.e * expert_stride +
-                                      (size_t)ti.mt * k_stages * CHUNK_BYTES;
+                                      (size_t)ti.mt0 * k_stages * CHUNK_BYTES;
                 for (int ks = 0; ks < k_stages; ks++) {
                     ok = mbar_wait(bar_w_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
                     if (!ok)
                         break;
-                    mbar_expect_tx(bar_w_full(s), W_SLOT_BYTES);
-                    bulk_load(smem_u32(w_ring + s * W_SLOT_BYTES), wsrc + (size_t)ks * CHUNK_BYTES,
-                              W_SLOT_BYTES, bar_w_full(s));
+                    mbar_expect_tx(bar_w_full(s), (uint32_t)(ti.n_mt * CHUNK_BYTES));
+                    for (int j = 0; j < ti.n_mt; j++)
+                        bulk_load(smem_u32(w_ring + s * W_SLOT_BYTES + j * CHUNK_BYTES),
+                                  wsrc + ((size_t)j * k_stages + ks) * CHUNK_BYTES, CHUNK_BYTES,
+                                  bar_w_full(s));
                     armed = min(armed + 1, WS);
                     RING_ADVANCE(s, ph, WS);
                 }
@@ -433,7 +465,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, m_items, tt, E);
                 for (int ks = 0; ks < k_stages; ks++) {
                     ok = mbar_wait(bar_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
                     if (!ok)
@@ -444,10 +476,6 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                     RING_ADVANCE(s, ph, STAGES);
                 }
             }
-            // after an abort the copies in flight complete on `full` barriers whose other
-            // arrivals may never come; the common exit below gives them time to land
-            if (!ok)
-                drain_wait(bar_full(s), ph ^ 1u);
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ----------------------------
@@ -457,14 +485,14 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             bool ok = true;
             int it = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
-                const int ab = it & 1;
-                ok = mbar_wait(bar_tmem_empty(ab), (uint32_t)((it >> 1) & 1) ^ 1u, status,
+                const TileInfo ti = decode_tile<BN>(tile, m_tiles, m_items, tt, E);
+                const int set = it % SETS, round = it / SETS;
+                ok = mbar_wait(bar_tmem_empty(set), (uint32_t)(round & 1) ^ 1u, status,
                                DS_TIMEOUT_TMEM_EMPTY, abort_flag);
                 if (!ok)
                     break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(ab * ACC_COLS);
+                const uint32_t d_set = tmem_base + (uint32_t)(set * SET_COLS);
                 const uint32_t idesc = make_idesc(ti.n_mma);
                 for (int ks = 0; ks < k_stages; ks++) {
                     ok = mbar_wait(bar_full(s), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
@@ -474,129 +502,145 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                     const uint64_t a_desc = make_sw128_desc(smem_u32(a_ring + s * A_SLOT_BYTES));
                     const uint64_t b_desc = make_sw128_desc(smem_u32(b_ring + s * B_SLOT_BYTES));
 #pragma unroll
-                    for (int kk = 0; kk < KSTAGE / 16; kk++) {
-                        // K-split: MMA kk goes to accumulator kk % NACC; each accumulator's
-                        // first MMA of the tile overwrites
-                        const int acc = kk % NACC;
-                        const uint32_t first = (ks == 0 && kk < NACC) ? 0u : 1u;
-                        umma_bf16(d_tmem + (uint32_t)(acc * BN), a_desc + (uint64_t)(kk * 2),
-                                  b_desc + (uint64_t)(kk * 2), idesc, first);
+                    for (int j = 0; j < MT; j++) {
+                        if (j < ti.n_mt) {
+#pragma unroll
+                            for (int kk = 0; kk < KSTAGE / 16; kk++) {
+                                // K-split: MMA kk goes to accumulator kk % NACC of weight tile
+                                // j; each accumulator's first MMA of the work item overwrites
+                                const int acc = j * NACC + kk % NACC;
+                                const uint32_t accumulate = (ks == 0 && kk < NACC) ? 0u : 1u;
+                                umma_bf16(d_set + (uint32_t)(acc * BN),
+                                          a_desc + (uint64_t)(j * (A_TILE_BYTES >> 4) + kk * 2),
+                                          b_desc + (uint64_t)(kk * 2), idesc, accumulate);
+                            }
+                        }
                     }
                     umma_commit(bar_empty(s));  // frees the slot when these MMAs have read it
                     RING_ADVANCE(s, ph, STAGES);
                 }
                 if (ok)
-                    umma_commit(bar_tmem_full(ab));
+                    umma_commit(bar_tmem_full(set));
             }
         }
     } else if (warp < EPI_WARP0) {
         // ------------------------------ MXFP4 decode --------------------------
         // DEQ_GROUPS groups of 4 warps; group g decodes the pipeline steps
-        // g, g + DEQ_GROUPS, ... into AB slot g, so that several steps are in
-        // flight at once (one step is a chain of waits, loads and dependent ALU
-        // instructions, longer than the MMAs of a step).  A thread owns one weight
-        // row of the tile and decodes both of its 32-column blocks.
+        // g, g + DEQ_GROUPS, ... so that several steps are in flight at once (one
+        // step is a chain of waits, loads and dependent ALU instructions, longer
+        // than the MMAs of a step).  A thread owns row r of each weight tile of
+        // the work item and decodes both of its 32-column blocks.
         const int u = threadIdx.x - DEQ_WARP0 * 32;
-        const int g = u >> 7;            // group = AB slot
-        const int r = u & (TILE_M - 1);  // weight row inside the tile
+        const int g = u >> 7;
+        const int r = u & (TILE_M - 1);
         const uint32_t a_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
         const int my_tiles = (int)blockIdx.x < total_tiles
                                  ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
         const int total_steps = my_tiles * k_stages;
         bool ok = true;
+        int cached_lt = -1, n_mt = MT;
         for (int i = g; ok && i < total_steps; i += DEQ_GROUPS) {
-            const int sw = i % WS;
+            if (MT > 1) {
+                const int lt = i / k_stages;
+                if (lt != cached_lt) {
+                    cached_lt = lt;
+                    n_mt = decode_tile<BN>((int)blockIdx.x + lt * (int)gridDim.x, m_tiles, m_items, tt, E).n_mt;
+                }
+            }
+            const int sw = i % WS, sa = i % STAGES;
             const uint32_t phw = (uint32_t)(i / WS) & 1u, pha = (uint32_t)(i / STAGES) & 1u;
-            ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag);
+            ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag) &&
+                 mbar_wait(bar_empty(sa), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
-            const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
-            const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
-            const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
-            const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
-            const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu), mult1 = mxfp4_scale_mult(sc >> 8);
-            const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            uint32_t d[8][4];
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-                mxfp4_decode_word(w[j], j < 4 ? mult0 : mult1, d[j]);
-            // the packed chunk is in registers now.  One arrival per warp: hundreds
-            // of per-thread arrivals on one mbarrier serialise in shared memory
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(bar_w_empty(sw));
-
-            ok = mbar_wait(bar_empty(g), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok)
-                break;
-            unsigned char* arow = a_ring + g * A_SLOT_BYTES + a_row_off;
+            for (int j = 0; j < MT; j++) {
+                if (j < n_mt) {
+                    const unsigned char* wst = w_ring + sw * W_SLOT_BYTES + j * CHUNK_BYTES;
+                    const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
+                    const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
+                    const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
+                    const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu);
+                    const uint32_t mult1 = mxfp4_scale_mult(sc >> 8);
+                    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                    unsigned char* arow = a_ring + sa * A_SLOT_BYTES + j * A_TILE_BYTES + a_row_off;
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int chunk = j ^ (r & 7);
-                *reinterpret_cast<uint4*>(arow + chunk * 16) =
-                    make_uint4(d[j][0], d[j][1], d[j][2], d[j][3]);
+                    for (int c = 0; c < 8; c++) {
+                        uint32_t d[4];
+                        mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d);
+                        *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) * 16)) =
+                            make_uint4(d[0], d[1], d[2], d[3]);
+                    }
+                }
             }
             fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive(bar_full(g));
+            // one arrival per warp: hundreds of per-thread arrivals on one mbarrier
+            // serialise in shared memory
+            if (lane == 0) {
+                mbar_arrive(bar_full(sa));
+                mbar_arrive(bar_w_empty(sw));
+            }
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        const int q = warp & 3;             // TMEM lane quarter this warp may read
-        const int row = q * 32 + lane;      // row inside the weight tile
+        const int j = (warp - EPI_WARP0) >> 2;  // weight tile of the work item this warp drains
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;          // row inside the weight tile
         bool ok = true;
         int it = 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-            const TileInfo ti = decode_tile<BN>(tile, m_tiles, tt, E);
-            const int ab = it & 1;
-            ok = mbar_wait(bar_tmem_full(ab), (uint32_t)((it >> 1) & 1), status,
-                           DS_TIMEOUT_TMEM_FULL, abort_flag);
+            const TileInfo ti = decode_tile<BN>(tile, m_tiles, m_items, tt, E);
+            const int set = it % SETS, round = it / SETS;
+            ok = mbar_wait(bar_tmem_full(set), (uint32_t)(round & 1), status, DS_TIMEOUT_TMEM_FULL,
+                           abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
             tc_fence_after();
-            const float* be = bias + (size_t)ti.e * bias_stride;
-            const int m = ti.mt * TILE_M + row;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * ACC_COLS);
-            if (MODE == 0) {
-                uint16_t* h = static_cast<uint16_t*>(outp);
-                const float bm = be[m];  // 2I is a multiple of TILE_M: always in range
-                const int jf = m >> 1;   // feature of this gate/up pair
-                const bool odd = (lane & 1) != 0;
-                for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
-                    float v[32];
-                    tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
+            if (j < ti.n_mt) {
+                const float* be = bias + (size_t)ti.e * bias_stride;
+                const int m = (ti.mt0 + j) * TILE_M + row;
+                const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) +
+                                        (uint32_t)(set * SET_COLS + j * NACC * BN);
+                if (MODE == 0) {
+                    uint16_t* h = static_cast<uint16_t*>(outp);
+                    const float bm = be[m];  // 2I is a multiple of TILE_M: always in range
+                    const int jf = m >> 1;   // feature of this gate/up pair
+                    const bool odd = (lane & 1) != 0;
+                    for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
+                        float v[32];
+                        tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        // even lane = gate row, odd lane = the matching up row: the even
-                        // lane finishes columns c0+j, the odd lane columns c0+16+j
-                        const float mine_lo = v[j] + bm, mine_hi = v[j + 16] + bm;
-                        const float send = odd ? mine_lo : mine_hi;
-                        const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-                        const float gate = odd ? recv : mine_lo;
-                        const float up = odd ? mine_hi : recv;
-                        const int col = c0 + j + (odd ? 16 : 0);
-                        if (col < ti.valid_n && jf < out_rows_valid)
-                            h[(size_t)(ti.row0 + col) * out_ld + jf] =
-                                (uint16_t)float_to_bf16_bits(swiglu(gate, up, alpha, limit));
+                        for (int c = 0; c < 16; c++) {
+                            // even lane = gate row, odd lane = the matching up row: the even
+                            // lane finishes columns c0+c, the odd lane columns c0+16+c
+                            const float mine_lo = v[c] + bm, mine_hi = v[c + 16] + bm;
+                            const float send = odd ? mine_lo : mine_hi;
+                            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                            const float gate = odd ? recv : mine_lo;
+                            const float up = odd ? mine_hi : recv;
+                            const int col = c0 + c + (odd ? 16 : 0);
+                            if (col < ti.valid_n && jf < out_rows_valid)
+                                h[(size_t)(ti.row0 + col) * out_ld + jf] =
+                                    (uint16_t)float_to_bf16_bits(swiglu(gate, up, alpha, limit));
+                        }
                     }
-                }
-            } else {
-                float* y = static_cast<float*>(outp);
-                const bool m_ok = m < out_rows_valid;
-                const float bm = m_ok ? be[m] : 0.f;
-                for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
-                    float v[32];
-                    tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
+                } else {
+                    float* y = static_cast<float*>(outp);
+                    const bool m_ok = m < out_rows_valid;
+                    const float bm = m_ok ? be[m] : 0.f;
+                    for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
+                        float v[32];
+                        tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int col = c0 + j;
-                        if (col < ti.valid_n && m_ok) {
-                            const int dst = row_dst ? row_dst[ti.row0 + col] : (ti.row0 + col);
-                            y[(size_t)dst * out_ld + m] = v[j] + bm;
+                        for (int c = 0; c < 32; c++) {
+                            const int col = c0 + c;
+                            if (col < ti.valid_n && m_ok) {
+                                const int dst = row_dst ? row_dst[ti.row0 + col] : (ti.row0 + col);
+                                y[(size_t)dst * out_ld + m] = v[c] + bm;
+                            }
                         }
                     }
                 }
@@ -604,7 +648,7 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
-                mbar_arrive(bar_tmem_empty(ab));
+                mbar_arrive(bar_tmem_empty(set));
         }
     }
 

@@ -191,6 +191,14 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
             h->cfg.n_experts, h->cfg.experts_per_token, score_out, h->topk_i, h->topk_w, h->blk_hist);
         return MOE_B200_OK;
     }
+    if constexpr (NT <= 4) {
+        // up to 128 experts: the tensor-core router (static shared memory)
+        route_mma_kernel<NT><<<nblk, RTHREADS, 0, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T,
+                                                        h->cfg.hidden_dim, lw.w_router, lw.b_router,
+                                                        h->cfg.n_experts, h->cfg.experts_per_token,
+                                                        score_out, h->topk_i, h->topk_w, h->blk_hist);
+        return MOE_B200_OK;
+    }
     const size_t smem = route_smem_bytes<NT>();
     if (!(h->smem_attr_done & 16) && smem > 48 * 1024) {
         CU_TRY(h, cudaFuncSetAttribute(route_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -220,12 +228,12 @@ moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5:
         h->smem_attr_done |= bit;
     }
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
-    tc5::expert_gemm_tc5_kernel<0, BN><<<h->n_sms, tc5::THREADS, smem, st>>>(
+    tc5::expert_gemm_tc5_kernel<0, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
         maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
         EL, h->hbuf, I, I, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
-    tc5::expert_gemm_tc5_kernel<1, BN><<<h->n_sms, tc5::THREADS, smem, st>>>(
+    tc5::expert_gemm_tc5_kernel<1, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
         h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
         EL, yout, H, H, row_dst, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);

@@ -373,4 +373,168 @@ route_small_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
         blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
 }
 
+// ---------------------------------------------------------------------------
+// Large-batch variant on the warp-level tensor-core path (mma.sync bf16, fp32
+// accumulate): the router is 0.4 % of the block's FLOPs but at 16k tokens x 128
+// experts it is 6 GFMA, too much for the fp32 pipes.
+//
+// Exactness of the expert indices: products of bf16 values are exact; what
+// differs from the CPU engine's double sum is the accumulation.  The tensor core
+// sums one K chunk of RMK = 64 terms into a fresh accumulator; the chunk results
+// are added to a running fp32 sum with round-to-nearest adds on the CUDA cores,
+// so no long accumulation happens inside the tensor core.  The index test
+// against the oracle (ties within 1e-6 excluded) is what admits this kernel.
+constexpr int RMK = 64;          // K chunk
+constexpr int RMLD = RMK + 8;    // bf16 per smem row: conflict-free fragment loads
+
+__device__ __forceinline__ void route_mma_16816(float c[4], const uint32_t a[4], const uint32_t b[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int NT>
+__global__ void __launch_bounds__(RTHREADS)
+route_mma_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
+                 const uint16_t* __restrict__ w_router, const float* __restrict__ b_router, int E,
+                 int K, float* __restrict__ score_out, int* __restrict__ topk_i,
+                 float* __restrict__ topk_w, int* __restrict__ blk_hist) {
+    constexpr int EP = NT * 32;      // padded expert count
+    constexpr int NTW = NT * 2;      // n8 tiles per warp (half of the experts)
+    constexpr size_t tiles_b = (size_t)(RB + EP) * RMLD * 2;
+    constexpr size_t lg_b = (size_t)RB * EP * 4;
+    __shared__ __align__(16) unsigned char smem_raw[(tiles_b > lg_b ? tiles_b : lg_b)];
+    __shared__ int hist[256];
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);  // [RB][RMLD]
+    uint16_t* ws = xs + RB * RMLD;                         // [EP][RMLD]
+    float* lg = reinterpret_cast<float*>(smem_raw);        // [RB][EP] after the GEMM
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int mb = warp & 3, nh = warp >> 2;
+    const int t0 = blockIdx.x * RB;
+    for (int i = tid; i < 256; i += RTHREADS)
+        hist[i] = 0;
+
+    float run[NTW][4];
+#pragma unroll
+    for (int n = 0; n < NTW; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            run[n][i] = 0.f;
+
+    // staging registers: 16-byte segments of the next chunk
+    constexpr int XSEG = RB * 8 / RTHREADS;  // 2
+    constexpr int WSEG = EP * 8 / RTHREADS;  // NT
+    uint4 xr[XSEG], wr[WSEG];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int s = 0; s < XSEG; s++) {
+            const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
+            uint4 q = make_uint4(0, 0, 0, 0);
+            if (t0 + row < T) {
+                if (x_is_f32) {
+                    const float4* p = reinterpret_cast<const float4*>(
+                        static_cast<const float*>(x) + (size_t)(t0 + row) * H + k0 + sg * 8);
+                    const float4 a = p[0], b = p[1];
+                    q = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
+                                   pack_bf16x2(b.z, b.w));
+                } else {
+                    q = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) +
+                                                        (size_t)(t0 + row) * H + k0 + sg * 8);
+                }
+            }
+            xr[s] = q;
+        }
+#pragma unroll
+        for (int s = 0; s < WSEG; s++) {
+            const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
+            wr[s] = (row < E) ? *reinterpret_cast<const uint4*>(w_router + (size_t)row * H + k0 + sg * 8)
+                              : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int s = 0; s < XSEG; s++) {
+            const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
+            *reinterpret_cast<uint4*>(xs + row * RMLD + sg * 8) = xr[s];
+        }
+#pragma unroll
+        for (int s = 0; s < WSEG; s++) {
+            const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
+            *reinterpret_cast<uint4*>(ws + row * RMLD + sg * 8) = wr[s];
+        }
+    };
+
+    const int n_chunks = H / RMK;  // H is a multiple of 64
+    fetch(0);
+    for (int c = 0; c < n_chunks; c++) {
+        __syncthreads();
+        stash();
+        __syncthreads();
+        if (c + 1 < n_chunks)
+            fetch((c + 1) * RMK);
+        float acc[NTW][4];
+#pragma unroll
+        for (int n = 0; n < NTW; n++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                acc[n][i] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < RMK / 16; kk++) {
+            uint32_t af[4];
+            const uint16_t* pa = xs + (mb * 16 + g) * RMLD + kk * 16 + 2 * t4;
+            af[0] = *reinterpret_cast<const uint32_t*>(pa);
+            af[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * RMLD);
+            af[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
+            af[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * RMLD + 8);
+#pragma unroll
+            for (int n = 0; n < NTW; n++) {
+                const uint16_t* pb = ws + (nh * (EP / 2) + n * 8 + g) * RMLD + kk * 16 + 2 * t4;
+                uint32_t bf[2];
+                bf[0] = *reinterpret_cast<const uint32_t*>(pb);
+                bf[1] = *reinterpret_cast<const uint32_t*>(pb + 8);
+                route_mma_16816(acc[n], af, bf);
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NTW; n++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                run[n][i] += acc[n][i];
+    }
+    __syncthreads();  // tiles dead; lg aliases them
+#pragma unroll
+    for (int n = 0; n < NTW; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int row = mb * 16 + g + 8 * (i >> 1);
+            const int e = nh * (EP / 2) + n * 8 + 2 * t4 + (i & 1);
+            lg[row * EP + e] = (e < E) ? run[n][i] + b_router[e] : -INFINITY;
+        }
+    __syncthreads();
+    if (score_out) {
+        for (int i = tid; i < RB * E; i += RTHREADS) {
+            const int r = i / E, e = i - r * E;
+            if (t0 + r < T)
+                score_out[(size_t)(t0 + r) * E + e] = lg[r * EP + e];
+        }
+    }
+    for (int r = warp; r < RB; r += RTHREADS / 32) {
+        const int t = t0 + r;
+        if (t >= T)
+            break;
+        float v[NT];
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+            v[j] = lg[r * EP + lane + 32 * j];
+        select_topk_softmax<NT>(v, lane, K, t, topk_i, topk_w, hist);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += RTHREADS)
+        blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
 }  // namespace moe

@@ -225,3 +225,25 @@ def test_forward_host_matches_device_path():
         out = torch.empty(50, 128, dtype=torch.float32).pin_memory()
         eng.forward_host(0, t.pin_memory(), out)
         assert torch.equal(out, dev)
+
+
+def test_router_indices_at_full_width_large_batch():
+    """The tensor-core router (batches above the small-batch threshold) at the
+    real hidden size and 128 experts: indices against the CPU engine's
+    double-accumulated router, ties within 1e-6 excluded."""
+    from parity_util import tie_mask
+
+    shape = pkg.MoEShape(hidden=2880, intermediate=64, n_experts=128, top_k=4)
+    lw = synth.make_layer(shape, seed=77)
+    T = 4096
+    x_bits = synth.make_tokens(T, shape.hidden, seed=77)
+    scores, ti, tv = oracle.route(synth.bf16_bits_to_f32(x_bits), synth.bf16_bits_to_f32(lw.w_router),
+                                  lw.b_router, 4, round_mode=1)
+    res = run_gpu(shape, lw, x_bits, capi.GEMM_TCGEN05)
+    ok = ~tie_mask(scores, 4)
+    err = np.abs(res["score"] - scores).max()
+    mism = int((res["topk_i"][ok] != ti[ok]).any(axis=1).sum())
+    print("router: max |logit error|", err, "ties excluded", int((~ok).sum()), "mismatches", mism)
+    assert mism == 0
+    assert err < 2e-6
+    assert np.abs(res["topk_w"][ok] - tv[ok]).max() < 1e-5
