@@ -22,7 +22,7 @@ SYMBOLS = [
     "moe_b200_last_error", "moe_b200_device_status", "moe_b200_last_launch_count",
     "moe_b200_last_expert_counts", "moe_b200_mxfp4_unpack", "moe_b200_unpack_resident",
     "moe_b200_version", "moe_b200_profile", "moe_b200_profile_read",
-    "moe_b200_last_intermediate",
+    "moe_b200_last_intermediate", "moe_b200_route_noalloc",
 ]
 N_STAGES = 9
 STAGE_NAMES = ["route", "plan", "permute", "dispatch", "regroup", "gemm1", "gemm2", "return",
@@ -84,6 +84,7 @@ def lib() -> ctypes.CDLL:
         L.moe_b200_unpack_resident.argtypes = [vp, ci, ci, ci, vp, vp]
         L.moe_b200_version.restype = ctypes.c_char_p
         L.moe_b200_last_intermediate.argtypes = [vp, ci, vp, vp]
+        L.moe_b200_route_noalloc.argtypes = [vp, ci, ci, ci, vp, vp, ci, ci, vp, vp, vp, vp, vp]
         L.moe_b200_profile.argtypes = [vp, ci]
         L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
         _lib = L

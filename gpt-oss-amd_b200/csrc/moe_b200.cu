@@ -779,6 +779,121 @@ moe_b200_status moe_b200_last_intermediate(moe_b200_handle h, int n_tokens, uint
     return MOE_B200_OK;
 }
 
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// moe_b200_route_noalloc: the routing kernels with their scratch in the library
+// image instead of a handle's workspace.
+
+namespace {
+
+constexpr int NA_MAX_BLOCKS = MOE_B200_ROUTE_NOALLOC_MAX_TOKENS / RBS;  // routing blocks of RBS tokens
+constexpr int NA_HIST_INTS = NA_MAX_BLOCKS * MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS;
+constexpr int NA_SCRATCH_INTS = 2 * NA_HIST_INTS + MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS + 1;
+constexpr int NA_MAX_DEVICES = 64;
+
+// [0, NA_HIST_INTS)              per-block expert histograms (router kernel -> plan kernel)
+// [NA_HIST_INTS, 2*NA_HIST_INTS) per-block row bases (written by the plan kernel, unused here)
+// [2*NA_HIST_INTS, ...)          tile table of the plan kernel (unused here)
+// About 0.5 MB per GPU.  In host code this name is only a stand-in for the
+// symbol, not a device address: kernels get the pointer cudaGetSymbolAddress
+// returns for the current device.
+static __device__ __align__(256) int g_route_noalloc_scratch[NA_SCRATCH_INTS];
+
+int* g_na_scratch_ptr[NA_MAX_DEVICES];  // per device, filled by the first call there
+int g_na_attr_done[NA_MAX_DEVICES];     // bit per router-kernel instantiation
+
+template <int NT>
+moe_b200_status route_noalloc_launch(int dev, const void* t, int t_dtype, int T, int H,
+                                     const uint16_t* w, const float* b, int E, int K, int* topk_i,
+                                     float* topk_w, int* counts, int* offsets, cudaStream_t st) {
+    const size_t smem = route_small_smem_bytes(H);
+    const int bit = NT == 1 ? 1 : NT == 2 ? 2 : NT == 4 ? 4 : 8;
+    if (!(g_na_attr_done[dev] & bit)) {
+        CU_TRY(nullptr, cudaFuncSetAttribute(route_small_kernel<NT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)route_small_smem_bytes(MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN)));
+        g_na_attr_done[dev] |= bit;
+    }
+    int* scratch = g_na_scratch_ptr[dev];
+    int* blk_hist = scratch;
+    int* blk_base = scratch + NA_HIST_INTS;
+    int* tile_start = scratch + 2 * NA_HIST_INTS;
+    const int nblk = ceil_div(T, RBS);
+    route_small_kernel<NT><<<nblk, RBS * 32, smem, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, w, b, E,
+                                                        K, nullptr, topk_i, topk_w, blk_hist);
+    plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, E, 1, counts, offsets, tile_start, blk_base);
+    CU_TRY(nullptr, cudaGetLastError());
+    return MOE_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens, int hidden_dim,
+                                       const void* w_router_bf16, const float* b_router,
+                                       int n_experts, int experts_per_token, int* topk_i_out,
+                                       float* topk_w_out, int* expert_counts_out,
+                                       int* expert_offsets_out, moe_b200_stream stream) {
+    if (!t || !w_router_bf16 || !b_router || !topk_i_out || !topk_w_out || !expert_counts_out ||
+        !expert_offsets_out)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "moe_b200_route_noalloc: null pointer");
+    if (t_dtype != MOE_B200_DTYPE_F32 && t_dtype != MOE_B200_DTYPE_BF16)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "moe_b200_route_noalloc: unknown activation dtype");
+    if (n_tokens <= 0 || n_tokens > MOE_B200_ROUTE_NOALLOC_MAX_TOKENS)
+        return fail(nullptr, MOE_B200_ERR_INVALID,
+                    "moe_b200_route_noalloc: n_tokens must be in 1.." +
+                        std::to_string(MOE_B200_ROUTE_NOALLOC_MAX_TOKENS) +
+                        " (the scratch array is fixed-size; use a handle for larger batches)");
+    if (n_experts <= 0 || n_experts > MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS)
+        return fail(nullptr, MOE_B200_ERR_INVALID,
+                    "moe_b200_route_noalloc: n_experts must be in 1.." +
+                        std::to_string(MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS));
+    if (hidden_dim <= 0 || hidden_dim % 64 || hidden_dim > MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN)
+        return fail(nullptr, MOE_B200_ERR_INVALID,
+                    "moe_b200_route_noalloc: hidden_dim must be a multiple of 64 up to " +
+                        std::to_string(MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN));
+    if (experts_per_token <= 0 || experts_per_token > 8 || experts_per_token > n_experts)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "moe_b200_route_noalloc: K must be in 1..min(8, n_experts)");
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(nullptr, MOE_B200_ERR_NO_DEVICE, "no CUDA device; this library has no CPU path");
+    }
+    if (dev < 0 || dev >= NA_MAX_DEVICES)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "moe_b200_route_noalloc: device ordinal too large");
+    if (!g_na_scratch_ptr[dev]) {
+        // set-up, once per device, with that device current: the symbol's address there
+        int* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail(nullptr, e == cudaErrorNoDevice ? MOE_B200_ERR_NO_DEVICE : MOE_B200_ERR_CUDA,
+                        std::string("cudaGetSymbolAddress(route scratch): ") + cudaGetErrorString(e));
+        }
+        g_na_scratch_ptr[dev] = p;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const uint16_t* w = static_cast<const uint16_t*>(w_router_bf16);
+    const int nt = ceil_div(n_experts, 32);
+    if (nt <= 1)
+        return route_noalloc_launch<1>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
+                                       experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
+                                       expert_offsets_out, st);
+    if (nt <= 2)
+        return route_noalloc_launch<2>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
+                                       experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
+                                       expert_offsets_out, st);
+    if (nt <= 4)
+        return route_noalloc_launch<4>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
+                                       experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
+                                       expert_offsets_out, st);
+    return route_noalloc_launch<8>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
+                                   experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
+                                   expert_offsets_out, st);
+}
+
 moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local_expert, int which,
                                          uint16_t* out_bf16, moe_b200_stream stream) {
     moe_b200_status st = check_layer(h, layer);

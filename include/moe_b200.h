@@ -210,6 +210,44 @@ moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local
 moe_b200_status moe_b200_last_intermediate(moe_b200_handle h, int n_tokens, uint16_t* out_bf16,
                                            moe_b200_stream stream);
 
+/* Routing without any allocation.  (No counterpart in the reference: its
+ * router, top-k and histogram kernels write into buffers that
+ * copy_transformer_to_device allocated beforehand.)
+ *
+ * For callers that cannot allocate device memory when they need a routing
+ * decision: an engine that gave its whole memory budget to its own pools during
+ * warm-up and must not meet cudaMalloc's device-wide synchronisation between
+ * decode steps, or a host that only lets a plug-in touch the buffers it is
+ * handed.  The call needs no handle and creates nothing: router GEMM + bias,
+ * top-k, softmax and the per-expert histogram / offsets run with their scratch
+ * (the per-block histograms) in a fixed array inside the library image, about
+ * 0.5 MB, which every GPU that loads the library holds until the process exits.
+ *
+ *   t                  device [n_tokens, hidden_dim], f32 or bf16
+ *   w_router_bf16      device bf16 [n_experts, hidden_dim];  b_router device f32 [n_experts]
+ *   topk_i_out         device i32 [n_tokens, K]   topk_w_out  device f32 [n_tokens, K]
+ *   expert_counts_out  device i32 [n_experts]     rows routed to each expert
+ *   expert_offsets_out device i32 [n_experts + 1] their exclusive prefix sum
+ * All five outputs are required.  Limits (MOE_B200_ERR_INVALID beyond them):
+ * n_tokens <= MOE_B200_ROUTE_NOALLOC_MAX_TOKENS, n_experts <=
+ * MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS, hidden_dim a multiple of 64 and <=
+ * MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN, K <= 8.
+ *
+ * The first call on a device looks up the array's device address and raises the
+ * kernels' shared-memory limit; make that first call before any stream capture.
+ * All calls on a device share the one array: it keeps the previous call's
+ * contents (every entry a call reads is written by that call first, so nothing
+ * has to be cleared), and two calls that overlap on the GPU -- different
+ * streams, or different host threads -- race on it. */
+#define MOE_B200_ROUTE_NOALLOC_MAX_TOKENS 2048
+#define MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS 256
+#define MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN 6144
+moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens, int hidden_dim,
+                                       const void* w_router_bf16, const float* b_router,
+                                       int n_experts, int experts_per_token, int* topk_i_out,
+                                       float* topk_w_out, int* expert_counts_out,
+                                       int* expert_offsets_out, moe_b200_stream stream);
+
 /* Library build info, e.g. "moe_b200 0.1 sm_100a". */
 const char* moe_b200_version(void);
 

@@ -1,0 +1,89 @@
+"""moe_b200_route_noalloc: routing with the scratch memory inside the library.
+
+Some callers of this library cannot allocate device memory at the moment they
+need a routing decision -- a serving loop that handed its whole memory budget
+to its own pools at warm-up and cannot afford the device-wide synchronisation
+of cudaMalloc between decode steps, or a host application that only lets a
+plug-in work on buffers it passes in.  For them the library has one entry point
+that needs no handle: the per-block histograms the routing kernels use as
+scratch live in a fixed array in the library image (about 0.5 MB per GPU, at
+most 2048 tokens and 256 experts per call).
+
+This test calls it through the C ABI twice in a row on different batches --
+the array keeps the first call's contents, and the second, smaller batch must
+not see them -- and compares expert indices, routing weights and per-expert
+counts with what the handle-based moe_b200_forward reports for the same inputs.
+It is the last test file on purpose, and passes on its own in a fresh process.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import gpt_oss_amd_b200 as pkg
+from gpt_oss_amd_b200 import capi, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _vp(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _route_noalloc(t, w_router, b_router, E, K):
+    T, H = t.shape
+    ti = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    tw = torch.empty(T, K, dtype=torch.float32, device="cuda")
+    cnt = torch.empty(E, dtype=torch.int32, device="cuda")
+    off = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    dt = capi.DTYPE_BF16 if t.dtype == torch.bfloat16 else capi.DTYPE_F32
+    s = torch.cuda.current_stream()
+    capi.check(capi.lib().moe_b200_route_noalloc(_vp(t), dt, T, H, _vp(w_router), _vp(b_router), E, K,
+                                                 _vp(ti), _vp(tw), _vp(cnt), _vp(off),
+                                                 ctypes.c_void_p(s.cuda_stream)))
+    torch.cuda.synchronize()
+    return ti.cpu().numpy(), tw.cpu().numpy(), cnt.cpu().numpy(), off.cpu().numpy()
+
+
+def test_route_noalloc_matches_forward_on_two_calls_in_a_row():
+    shape = pkg.MoEShape(hidden=256, intermediate=64, n_experts=40, top_k=4)
+    lw = synth.make_layer(shape, seed=31)
+    w_router = torch.from_numpy(lw.w_router.view(np.int16)).cuda()
+    b_router = torch.from_numpy(lw.b_router).cuda()
+    with pkg.MoEEngine(shape, max_tokens=1024) as eng:
+        eng.load_layer(0, lw)
+        for call, (T, seed, dtype) in enumerate([(1000, 1, torch.bfloat16), (37, 2, torch.float32)]):
+            x_bits = synth.make_tokens(T, shape.hidden, seed=seed)
+            t = torch.from_numpy(x_bits.view(np.int16)).cuda().view(torch.bfloat16).to(dtype)
+            _, _, ref_i, ref_w = eng.forward(0, t, side=True)
+            torch.cuda.synchronize()
+            ref_cnt = np.array(eng.last_expert_counts())
+            ti, tw, cnt, off = _route_noalloc(t, w_router, b_router, shape.n_experts, shape.top_k)
+            # same kernels on the same inputs: identical, not merely close
+            assert np.array_equal(ti, ref_i.cpu().numpy()), f"call {call}"
+            assert np.array_equal(tw, ref_w.cpu().numpy()), f"call {call}"
+            assert np.array_equal(cnt, ref_cnt), f"call {call}"
+            assert cnt.sum() == T * shape.top_k
+            assert np.array_equal(off, np.concatenate([[0], np.cumsum(cnt)])), f"call {call}"
+
+
+def test_route_noalloc_rejects_sizes_beyond_its_fixed_scratch():
+    t = torch.zeros(8, 128, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 128, dtype=torch.int16, device="cuda")
+    b = torch.zeros(8, dtype=torch.float32, device="cuda")
+    o = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    L = capi.lib()
+
+    def call(T=8, H=128, E=8, K=4):
+        return L.moe_b200_route_noalloc(_vp(t), capi.DTYPE_BF16, T, H, _vp(w), _vp(b), E, K, _vp(o),
+                                        _vp(o), _vp(o), _vp(o), None)
+
+    assert call(T=2049) == capi.ERR_INVALID
+    assert b"2048" in L.moe_b200_last_error(None)
+    assert call(E=257) == capi.ERR_INVALID
+    assert call(H=6208) == capi.ERR_INVALID
+    assert call(H=100) == capi.ERR_INVALID
+    assert call(K=9) == capi.ERR_INVALID
+    assert L.moe_b200_route_noalloc(None, capi.DTYPE_BF16, 8, 128, _vp(w), _vp(b), 8, 4, _vp(o), _vp(o),
+                                    _vp(o), _vp(o), None) == capi.ERR_INVALID
