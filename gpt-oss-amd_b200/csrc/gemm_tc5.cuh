@@ -14,26 +14,25 @@
 // the B operand (N = 16..BN columns), so a ragged expert only narrows N.
 //
 // Shared-memory rings:
-//   W ring   packed MXFP4 chunks (4352 B), deep: covers the HBM latency
+//   W ring   packed MXFP4 chunks (4352 B each), deep: covers the HBM latency
 //            bulk copy -> decode warps
 //   AB ring  STAGES slots, each a decoded bf16 weight tile (16 KB, written by
 //            the decode warps) plus an activation tile (BN x 128 B, written by
 //            TMA); ONE `full` barrier per slot collects the decode warps'
 //            arrivals and the TMA transaction bytes, ONE `empty` barrier per
-//            slot is signalled by tcgen05.commit -- the MMA-issuing thread does
-//            one wait and one commit per pipeline step, which is what bounds
-//            the step rate.
-// The kernel is instantiated for BN = 64, 128 and 256 token rows per tile.
-// Narrow tiles split the K loop over NACC accumulators in tensor memory (summed
-// in the epilogue): back-to-back MMAs into one accumulator are a dependent
-// chain whose latency, not throughput, bounds small-N tiles.
+//            slot is signalled by tcgen05.commit, so the MMA-issuing thread does
+//            one wait and one commit per pipeline step.
+// The kernel is instantiated for BN = 64, 128 and 256 token rows per tile (see
+// Geo<BN> below).  Narrow tiles split the K loop over NACC accumulators in
+// tensor memory (summed in the epilogue): back-to-back MMAs into one
+// accumulator are a dependent chain whose latency bounds small-N tiles.
 //
-// Warp roles (736 threads):
+// Warp roles:
 //   warp 0       W producer        warp 1   B producer (TMA)
 //   warp 2       allocates tensor memory, issues tcgen05.mma, commits
-//   warps 3-18   decode packed MXFP4 -> bf16 into the 128B-swizzled A slot,
-//                four groups of four warps working on four pipeline steps at once
-//   warps 19-22  epilogue: tcgen05.ld, bias, SwiGLU / store
+//   next 4*G     decode packed MXFP4 -> bf16 into the 128B-swizzled A slot, G
+//                groups of four warps working on G pipeline steps at once
+//   last 4*MT    epilogue: tcgen05.ld, bias, SwiGLU / store
 //
 // Every mbarrier wait is bounded in time; a wait that runs out records a code
 // in the handle's status word, raises a CTA-wide abort flag and all roles fall
@@ -549,38 +548,73 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             }
             const int sw = i % WS, sa = i % STAGES;
             const uint32_t phw = (uint32_t)(i / WS) & 1u, pha = (uint32_t)(i / STAGES) & 1u;
-            ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag) &&
-                 mbar_wait(bar_empty(sa), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+            ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
+            if (MT == 1) {
+                // decode into registers first, release the packed chunk, and only then
+                // wait for the A slot: the ALU work overlaps the MMAs still reading it
+                const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
+                const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
+                const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
+                const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
+                const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu);
+                const uint32_t mult1 = mxfp4_scale_mult(sc >> 8);
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                uint32_t d[8][4];
 #pragma unroll
-            for (int j = 0; j < MT; j++) {
-                if (j < n_mt) {
-                    const unsigned char* wst = w_ring + sw * W_SLOT_BYTES + j * CHUNK_BYTES;
-                    const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
-                    const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
-                    const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
-                    const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu);
-                    const uint32_t mult1 = mxfp4_scale_mult(sc >> 8);
-                    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                    unsigned char* arow = a_ring + sa * A_SLOT_BYTES + j * A_TILE_BYTES + a_row_off;
+                for (int c = 0; c < 8; c++)
+                    mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d[c]);
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(bar_w_empty(sw));
+                ok = mbar_wait(bar_empty(sa), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                unsigned char* arow = a_ring + sa * A_SLOT_BYTES + a_row_off;
 #pragma unroll
-                    for (int c = 0; c < 8; c++) {
-                        uint32_t d[4];
-                        mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d);
-                        *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) * 16)) =
-                            make_uint4(d[0], d[1], d[2], d[3]);
+                for (int c = 0; c < 8; c++)
+                    *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) * 16)) =
+                        make_uint4(d[c][0], d[c][1], d[c][2], d[c][3]);
+                fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(bar_full(sa));
+            } else {
+                ok = mbar_wait(bar_empty(sa), pha ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+#pragma unroll
+                for (int j = 0; j < MT; j++) {
+                    if (j < n_mt) {
+                        const unsigned char* wst = w_ring + sw * W_SLOT_BYTES + j * CHUNK_BYTES;
+                        const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
+                        const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
+                        const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
+                        const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu);
+                        const uint32_t mult1 = mxfp4_scale_mult(sc >> 8);
+                        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                        unsigned char* arow = a_ring + sa * A_SLOT_BYTES + j * A_TILE_BYTES + a_row_off;
+#pragma unroll
+                        for (int c = 0; c < 8; c++) {
+                            uint32_t d[4];
+                            mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d);
+                            *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) * 16)) =
+                                make_uint4(d[0], d[1], d[2], d[3]);
+                        }
                     }
                 }
-            }
-            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-            __syncwarp();
-            // one arrival per warp: hundreds of per-thread arrivals on one mbarrier
-            // serialise in shared memory
-            if (lane == 0) {
-                mbar_arrive(bar_full(sa));
-                mbar_arrive(bar_w_empty(sw));
+                fence_proxy_async_smem();
+                __syncwarp();
+                // one arrival per warp: hundreds of per-thread arrivals on one mbarrier
+                // serialise in shared memory
+                if (lane == 0) {
+                    mbar_arrive(bar_full(sa));
+                    mbar_arrive(bar_w_empty(sw));
+                }
             }
         }
     } else {
