@@ -148,6 +148,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "mma_sync"])
     ap.add_argument("--cpu-sample", type=int, default=16, help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel exchange: inside the kernels over NVLink peer memory, or NCCL")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the workload's tokens per step (for small profiling captures)")
     args = ap.parse_args()
@@ -213,9 +215,7 @@ def main():
     eng = pkg.MoEEngine(shape, n_layers=wl["L"], max_tokens=T_local, ep_rank=ep_rank, ep_size=ep,
                         device=local_rank, gemm_impl=gemm_impl)
     if ep > 1:
-        ids = [pkg.MoEEngine.ep_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(ids, src=0)
-        eng.ep_init(ids[0])
+        eng.ep_connect(dist, args.ep_exchange)
     for layer in range(wl["L"]):
         lw = synth.make_layer(shape, seed=layer, zipf_s=wl["zipf"], zipf_gain=ZIPF_GAIN,
                               first=eng.first_expert, n=eng.n_local)
@@ -350,6 +350,8 @@ def main():
             cpu["value"] = tps / wl["L"]
             cpu["sample"] += f"; reported per {wl['L']}-layer step"
 
+    if ep > 1:
+        config["ep_exchange"] = args.ep_exchange
     config.update({"parallelism": (f"ep{ep}" if ep > 1 else ("single" if world == 1 else f"replicas{world}")),
                    "tokens_per_rank": T_local, "experts_per_rank": eng.n_local,
                    "gemm_impl": "tcgen05" if gemm_impl == capi.GEMM_TCGEN05 else "mma_sync",

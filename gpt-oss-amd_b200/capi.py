@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libmoe_b200.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_NOT_LOADED, ERR_DEVICE, ERR_NCCL, ERR_UNSUPPORTED = range(8)
 DTYPE_F32, DTYPE_BF16 = 0, 1
 GEMM_TCGEN05, GEMM_MMA_SYNC = 0, 1
+EP_PEER_EXPORT_BYTES = 256
 
 #: every symbol include/moe_b200.h declares
 SYMBOLS = [
@@ -23,6 +24,7 @@ SYMBOLS = [
     "moe_b200_last_expert_counts", "moe_b200_mxfp4_unpack", "moe_b200_unpack_resident",
     "moe_b200_version", "moe_b200_profile", "moe_b200_profile_read",
     "moe_b200_last_intermediate", "moe_b200_route_noalloc",
+    "moe_b200_ep_peer_export", "moe_b200_ep_peer_enable",
 ]
 N_STAGES = 9
 STAGE_NAMES = ["route", "plan", "permute", "dispatch", "regroup", "gemm1", "gemm2", "return",
@@ -85,6 +87,8 @@ def lib() -> ctypes.CDLL:
         L.moe_b200_version.restype = ctypes.c_char_p
         L.moe_b200_last_intermediate.argtypes = [vp, ci, vp, vp]
         L.moe_b200_route_noalloc.argtypes = [vp, ci, ci, ci, vp, vp, ci, ci, vp, vp, vp, vp, vp]
+        L.moe_b200_ep_peer_export.argtypes = [vp, ctypes.c_char_p]
+        L.moe_b200_ep_peer_enable.argtypes = [vp, ctypes.c_char_p]
         L.moe_b200_profile.argtypes = [vp, ci]
         L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
         _lib = L

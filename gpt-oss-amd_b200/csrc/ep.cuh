@@ -22,6 +22,7 @@
 
 #include "../../include/moe_b200.h"
 #include "common.cuh"
+#include "ep_peer.cuh"
 
 namespace moe {
 namespace ep {
@@ -40,6 +41,18 @@ struct State {
     int* recv_off_dev = nullptr;  // [G]
     int* h_cnt_all = nullptr;     // pinned [G, E]
     std::vector<int> send_cnt, send_off, recv_cnt, recv_off;
+
+    // peer-memory mode (ep_peer.cuh)
+    int* ctrl = nullptr;          // [G*E counts][3*G flags]; cnt_all aliases its start
+    char* arena = nullptr;        // one allocation holding xgrp, yrecv, ctrl, ret (peer-visible)
+    size_t arena_off[4] = {0, 0, 0, 0};
+    int2* ret = nullptr;          // [rows_cap] return address of each received row
+    float** row_ptr = nullptr;    // [rows_cap] owner's result row for each row computed here
+    int* send_base = nullptr;     // [E] where this rank's rows of expert e start at the owner
+    peer::Table table{};
+    std::vector<void*> opened;    // cudaIpcOpenMemHandle mappings to close
+    bool peer_enabled = false;
+    int seq = 0;                  // call sequence number carried by the flags
 };
 
 typedef std::function<int(const uint16_t* xin, int rows_upper, int bn, const int* g_off,
@@ -162,17 +175,35 @@ inline int allocate(State& s, const moe_b200_config& c, int n_local, int first, 
     const size_t H = c.hidden_dim, E = c.n_experts, G = c.ep_size;
     const size_t TK = (size_t)c.max_tokens * c.experts_per_token;
     int st;
-    if ((st = ep_alloc(&s.cnt_all, G * E, allocs, bytes, err)) ||
+    // The buffers a peer writes (xgrp, yrecv, ctrl, ret) share ONE allocation, so that one
+    // IPC handle exports them and a peer maps them with one call.
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    s.arena_off[0] = 0;                                                      // xgrp
+    s.arena_off[1] = s.arena_off[0] + up((size_t)rows_cap * H * sizeof(uint16_t));  // yrecv
+    s.arena_off[2] = s.arena_off[1] + up(TK * H * sizeof(float));            // ctrl
+    s.arena_off[3] = s.arena_off[2] + up((G * E + 3 * G + 16) * sizeof(int));  // ret
+    const size_t arena_bytes = s.arena_off[3] + up((size_t)rows_cap * sizeof(int2));
+    if ((st = ep_alloc(&s.arena, arena_bytes, allocs, bytes, err)))
+        return st;
+    s.xgrp = reinterpret_cast<uint16_t*>(s.arena + s.arena_off[0]);
+    s.yrecv = reinterpret_cast<float*>(s.arena + s.arena_off[1]);
+    s.ctrl = reinterpret_cast<int*>(s.arena + s.arena_off[2]);
+    s.ret = reinterpret_cast<int2*>(s.arena + s.arena_off[3]);
+    if ((st = ep_alloc(&s.row_ptr, (size_t)rows_cap, allocs, bytes, err)) ||
+        (st = ep_alloc(&s.send_base, E, allocs, bytes, err)) ||
         (st = ep_alloc(&s.xrecv, (size_t)rows_cap * H, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.xgrp, (size_t)rows_cap * H, allocs, bytes, err)) ||
         (st = ep_alloc(&s.ysend, (size_t)rows_cap * H, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.yrecv, TK * H, allocs, bytes, err)) ||
         (st = ep_alloc(&s.g_cnt, n_local, allocs, bytes, err)) ||
         (st = ep_alloc(&s.g_off, n_local + 1, allocs, bytes, err)) ||
         (st = ep_alloc(&s.g_tile_start, n_local + 1, allocs, bytes, err)) ||
         (st = ep_alloc(&s.gather_src, rows_cap, allocs, bytes, err)) ||
         (st = ep_alloc(&s.recv_off_dev, G, allocs, bytes, err)))
         return st;
+    s.cnt_all = s.ctrl;
+    if (cudaMemset(s.ctrl, 0, (G * E + 3 * G + 16) * sizeof(int)) != cudaSuccess) {
+        err = "cudaMemset failed";
+        return MOE_B200_ERR_CUDA;
+    }
     if (cudaMallocHost(reinterpret_cast<void**>(&s.h_cnt_all), G * E * sizeof(int)) != cudaSuccess) {
         err = "cudaMallocHost failed";
         return MOE_B200_ERR_CUDA;
@@ -185,6 +216,10 @@ inline int allocate(State& s, const moe_b200_config& c, int n_local, int first, 
 }
 
 inline void shutdown(State& s) {
+    for (void* p : s.opened)
+        cudaIpcCloseMemHandle(p);
+    s.opened.clear();
+    s.peer_enabled = false;
     if (s.comm) {
         ncclCommDestroy(s.comm);
         s.comm = nullptr;
@@ -304,6 +339,67 @@ inline int exchange_and_compute(State& s, const moe_b200_config& c, int n_local,
     EP_NCCL(ncclGroupEnd());
     mark(MOE_B200_STAGE_RETURN, false);
     *y_out = s.yrecv;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Peer-memory mode
+
+constexpr int PEER_BUFFERS = 4;  // xgrp, yrecv, ctrl, ret
+static_assert(sizeof(cudaIpcMemHandle_t) == MOE_B200_EP_IPC_BYTES, "IPC handle size");
+
+// blob: the arena's IPC handle, then the four byte offsets (xgrp, yrecv, ctrl, ret) as u64.
+inline int peer_export(State& s, char* out, std::string& err) {
+    memset(out, 0, MOE_B200_EP_PEER_EXPORT_BYTES);
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == MOE_B200_EP_IPC_BYTES, "cudaIpcMemHandle_t is expected to be 64 bytes");
+    EP_CUDA(cudaIpcGetMemHandle(&h, s.arena));
+    memcpy(out, &h, sizeof(h));
+    unsigned long long off[PEER_BUFFERS];
+    for (int i = 0; i < PEER_BUFFERS; i++)
+        off[i] = s.arena_off[i];
+    memcpy(out + sizeof(h), off, sizeof(off));
+    return 0;
+}
+
+// all: [G][MOE_B200_EP_PEER_EXPORT_BYTES], the exports of every rank in rank order.
+inline int peer_enable(State& s, const moe_b200_config& c, const char* all, std::string& err) {
+    const int G = c.ep_size, rank = c.ep_rank;
+    if (G > peer::MAX_RANKS) {
+        err = "peer-memory mode supports at most 8 ranks";
+        return MOE_B200_ERR_UNSUPPORTED;
+    }
+    if (c.n_experts > 256) {
+        err = "peer-memory mode supports at most 256 experts";
+        return MOE_B200_ERR_UNSUPPORTED;
+    }
+    if (s.peer_enabled)
+        return 0;
+    for (int p = 0; p < G; p++) {
+        const char* blob = all + (size_t)p * MOE_B200_EP_PEER_EXPORT_BYTES;
+        unsigned long long off[PEER_BUFFERS];
+        memcpy(off, blob + MOE_B200_EP_IPC_BYTES, sizeof(off));
+        char* base = s.arena;
+        if (p != rank) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, blob, sizeof(h));
+            void* q = nullptr;
+            EP_CUDA(cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+            s.opened.push_back(q);
+            base = static_cast<char*>(q);
+        } else {
+            for (int i = 0; i < PEER_BUFFERS; i++)
+                if (off[i] != s.arena_off[i]) {
+                    err = "peer export blobs are not in rank order";
+                    return MOE_B200_ERR_INVALID;
+                }
+        }
+        s.table.xgrp[p] = reinterpret_cast<uint16_t*>(base + off[0]);
+        s.table.yrecv[p] = reinterpret_cast<float*>(base + off[1]);
+        s.table.ctrl[p] = reinterpret_cast<int*>(base + off[2]);
+        s.table.ret[p] = reinterpret_cast<int2*>(base + off[3]);
+    }
+    s.peer_enabled = true;
     return 0;
 }
 

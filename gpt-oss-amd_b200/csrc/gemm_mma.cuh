@@ -55,7 +55,8 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
                        const uint16_t* __restrict__ xin, int K, const int* __restrict__ g_off,
                        const int* __restrict__ g_cnt, const int* __restrict__ g_tile_start, int E,
                        void* __restrict__ outp, int out_ld, int out_rows_valid,
-                       const int* __restrict__ row_dst, float alpha, float limit) {
+                       const int* __restrict__ row_dst, float* const* __restrict__ row_ptr,
+                       float alpha, float limit) {
     __shared__ __align__(16) uint16_t As[TILE_M * V0_LD];
     __shared__ __align__(16) uint16_t Bs[V0_BN * V0_LD];
 
@@ -175,8 +176,10 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
                     for (int c = 0; c < 2; c++) {
                         const int col = nh * 32 + nb * 8 + 2 * t + c;
                         if (col < valid_n) {
-                            const int dst = row_dst ? row_dst[row0 + col] : (row0 + col);
-                            y[(size_t)dst * out_ld + m] = acc[a][nb][2 * half + c] + bm;
+                            float* yrow = row_ptr ? row_ptr[row0 + col]
+                                                  : y + (size_t)(row_dst ? row_dst[row0 + col]
+                                                                         : (row0 + col)) * out_ld;
+                            yrow[m] = acc[a][nb][2 * half + c] + bm;
                         }
                     }
             }

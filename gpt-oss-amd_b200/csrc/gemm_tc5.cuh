@@ -350,8 +350,9 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                        const float* __restrict__ bias, int bias_stride,
                        const int* __restrict__ g_off, const int* __restrict__ g_cnt,
                        const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
-                       int out_ld, int out_rows_valid, const int* __restrict__ row_dst, float alpha,
-                       float limit, int* __restrict__ status) {
+                       int out_ld, int out_rows_valid, const int* __restrict__ row_dst,
+                       float* const* __restrict__ row_ptr, float alpha, float limit,
+                       int* __restrict__ status) {
     constexpr int MT = Geo<BN>::MT, STAGES = Geo<BN>::STAGES, WS = Geo<BN>::WS;
     constexpr int NACC = Geo<BN>::NACC, SETS = Geo<BN>::SETS;
     constexpr int THREADS = n_threads<BN>();
@@ -672,8 +673,12 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                         for (int c = 0; c < 32; c++) {
                             const int col = c0 + c;
                             if (col < ti.valid_n && m_ok) {
-                                const int dst = row_dst ? row_dst[ti.row0 + col] : (ti.row0 + col);
-                                y[(size_t)dst * out_ld + m] = v[c] + bm;
+                                // result row: on another GPU (peer mode), at a remapped row
+                                // (received order), or in place
+                                float* yrow = row_ptr ? row_ptr[ti.row0 + col]
+                                                      : y + (size_t)(row_dst ? row_dst[ti.row0 + col]
+                                                                             : (ti.row0 + col)) * out_ld;
+                                yrow[m] = v[c] + bm;
                             }
                         }
                     }

@@ -215,7 +215,7 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
 template <int BN>
 moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
                            const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
-                           const int* row_dst, cudaStream_t st) {
+                           const int* row_dst, float* const* row_ptr, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
     constexpr int smem = tc5::smem_bytes<BN>();
@@ -230,12 +230,12 @@ moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5:
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
     tc5::expert_gemm_tc5_kernel<0, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
         maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-        EL, h->hbuf, I, I, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+        EL, h->hbuf, I, I, nullptr, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
     tc5::expert_gemm_tc5_kernel<1, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
         h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
-        EL, yout, H, H, row_dst, c.swiglu_alpha, c.swiglu_limit, h->status);
+        EL, yout, H, H, row_dst, row_ptr, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
     h->last_launches += 2;
     return MOE_B200_OK;
@@ -246,7 +246,7 @@ moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5:
 moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const uint16_t* xin,
                              const tc5::TensorMaps& maps_x, int rows_upper, int bn, const int* g_off,
                              const int* g_cnt, const int* g_tile_start, float* yout,
-                             const int* row_dst, cudaStream_t st) {
+                             const int* row_dst, float* const* row_ptr, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
     if (c.gemm_impl == MOE_B200_GEMM_MMA_SYNC) {
@@ -255,19 +255,21 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
         prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
         expert_gemm_mma_kernel<0><<<g1, 256, 0, st>>>(lw.w1, h->stride1, h->ks1, lw.bias1, 2 * I, xin,
                                                       H, g_off, g_cnt, g_tile_start, EL, h->hbuf, I,
-                                                      I, nullptr, c.swiglu_alpha, c.swiglu_limit);
+                                                      I, nullptr, nullptr, c.swiglu_alpha,
+                                                      c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
         prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
         expert_gemm_mma_kernel<1><<<g2, 256, 0, st>>>(lw.w2, h->stride2, h->ks2, lw.bias2, H, h->hbuf,
                                                       I, g_off, g_cnt, g_tile_start, EL, yout, H, H,
-                                                      row_dst, c.swiglu_alpha, c.swiglu_limit);
+                                                      row_dst, row_ptr, c.swiglu_alpha,
+                                                      c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
     } else if (bn == 64) {
-        return launch_tc5<64>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, st);
+        return launch_tc5<64>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
     } else if (bn == 128) {
-        return launch_tc5<128>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, st);
+        return launch_tc5<128>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
     } else {
-        return launch_tc5<256>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, st);
+        return launch_tc5<256>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
     }
     h->last_launches += 2;
     return MOE_B200_OK;
@@ -537,8 +539,10 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     for (char s : lw.expert_set)
         if (!s)
             return fail(h, MOE_B200_ERR_NOT_LOADED, "not every local expert of this layer was set");
-    if (c.ep_size > 1 && !h->ep.comm)
-        return fail(h, MOE_B200_ERR_NCCL, "ep_size > 1 but moe_b200_ep_init was not called");
+    if (c.ep_size > 1 && !h->ep.comm && !h->ep.peer_enabled)
+        return fail(h, MOE_B200_ERR_NCCL,
+                    "ep_size > 1 but neither moe_b200_ep_init nor moe_b200_ep_peer_enable was called");
+    const bool peer_mode = c.ep_size > 1 && h->ep.peer_enabled;
     CU_TRY(h, cudaSetDevice(c.device));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int T = n_tokens, H = c.hidden_dim, E = c.n_experts, K = c.experts_per_token;
@@ -571,7 +575,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
                                   h->blk_base);
     prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
     h->last_launches++;
-    if (T > 0) {
+    if (T > 0 && !peer_mode) {
         prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
         permute_kernel<<<nblk, 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb,
                                             h->topk_i, h->blk_base, h->slot_of, h->row_token, h->xs,
@@ -581,10 +585,40 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     }
 
     const float* y_for_combine = h->ybuf;
-    if (c.ep_size == 1) {
+    if (peer_mode) {
+        // exchange fused into the permute kernel and the down GEMM's epilogue (ep_peer.cuh)
+        ep::State& es = h->ep;
+        const int G = c.ep_size, rank = c.ep_rank;
+        const int seq = ++es.seq;
+        const int bn = pick_bn(h, (T > 0 ? T : c.max_tokens) * K);  // rows here are not known on the host
+        prof_mark(h, MOE_B200_STAGE_DISPATCH, true, s);
+        peer::publish_counts_kernel<<<1, 256, 0, s>>>(h->cnt, E, G, rank, es.table, seq);
+        peer::wait_counts_plan_kernel<<<1, 256, 0, s>>>(E, G, rank, bn, es.table, seq, es.g_cnt, es.g_off,
+                                                        es.g_tile_start, es.send_base, h->status);
+        if (T > 0)
+            peer::permute_to_peers_kernel<<<nblk, 256, 0, s>>>(
+                t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, G, rank, rb, h->topk_i, h->blk_base,
+                h->off, es.send_base, es.table, h->slot_of, h->status);
+        peer::barrier_kernel<<<1, 32, 0, s>>>(1, E, G, rank, es.table, seq, h->status);
+        prof_mark(h, MOE_B200_STAGE_DISPATCH, false, s);
+        prof_mark(h, MOE_B200_STAGE_REGROUP, true, s);
+        peer::row_pointers_kernel<<<h->n_sms, 256, 0, s>>>(es.g_off, h->n_local, H, es.table, rank,
+                                                           es.row_ptr);
+        prof_mark(h, MOE_B200_STAGE_REGROUP, false, s);
+        h->last_launches += (T > 0 ? 5 : 4);
+        st = launch_gemms(h, lw, es.xgrp, h->maps_x, h->rows_cap, bn, es.g_off, es.g_cnt,
+                          es.g_tile_start, nullptr, nullptr, es.row_ptr, s);
+        if (st)
+            return st;
+        prof_mark(h, MOE_B200_STAGE_RETURN, true, s);
+        peer::barrier_kernel<<<1, 32, 0, s>>>(2, E, G, rank, es.table, seq, h->status);
+        prof_mark(h, MOE_B200_STAGE_RETURN, false, s);
+        h->last_launches++;
+        y_for_combine = es.yrecv;
+    } else if (c.ep_size == 1) {
         if (T > 0) {
             st = launch_gemms(h, lw, h->xs, h->maps_x, T * K, bn_local, h->off, h->cnt, h->tile_start,
-                              h->ybuf, nullptr, s);
+                              h->ybuf, nullptr, nullptr, s);
             if (st)
                 return st;
         }
@@ -593,7 +627,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
                                   const int* g_cnt, const int* g_tile_start, float* yout,
                                   const int* row_dst) -> int {
             return (int)launch_gemms(h, lw, xin, h->maps_x, rows_upper, bn, g_off, g_cnt,
-                                     g_tile_start, yout, row_dst, s);
+                                     g_tile_start, yout, row_dst, nullptr, s);
         };
         ep::PickBn pick = [&](int rows) { return pick_bn(h, rows); };
         int launches = 0;
@@ -658,6 +692,24 @@ moe_b200_status moe_b200_ep_unique_id(char id_out[128]) {
     if (st)
         g_create_error = err;
     return st;
+}
+
+moe_b200_status moe_b200_ep_peer_export(moe_b200_handle h, char* blob_out) {
+    if (!h || !blob_out)
+        return MOE_B200_ERR_INVALID;
+    if (h->cfg.ep_size <= 1)
+        return fail(h, MOE_B200_ERR_INVALID, "handle was created with ep_size == 1");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    return (moe_b200_status)ep::peer_export(h->ep, blob_out, h->err);
+}
+
+moe_b200_status moe_b200_ep_peer_enable(moe_b200_handle h, const char* all_blobs) {
+    if (!h || !all_blobs)
+        return MOE_B200_ERR_INVALID;
+    if (h->cfg.ep_size <= 1)
+        return fail(h, MOE_B200_ERR_INVALID, "handle was created with ep_size == 1");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    return (moe_b200_status)ep::peer_enable(h->ep, h->cfg, all_blobs, h->err);
 }
 
 moe_b200_status moe_b200_ep_init(moe_b200_handle h, const char id[128]) {

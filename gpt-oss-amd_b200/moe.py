@@ -134,6 +134,28 @@ class MoEEngine:
     def ep_init(self, unique_id: bytes):
         capi.check(capi.lib().moe_b200_ep_init(self._h, unique_id), self._h)
 
+    def ep_peer_export(self) -> bytes:
+        buf = ctypes.create_string_buffer(capi.EP_PEER_EXPORT_BYTES)
+        capi.check(capi.lib().moe_b200_ep_peer_export(self._h, buf), self._h)
+        return buf.raw
+
+    def ep_peer_enable(self, blobs_in_rank_order: list[bytes]):
+        """Map the peers' exchange buffers: the exchange then runs inside the
+        kernels over NVLink peer memory instead of NCCL."""
+        capi.check(capi.lib().moe_b200_ep_peer_enable(self._h, b"".join(blobs_in_rank_order)), self._h)
+
+    def ep_connect(self, dist, mode: str = "peer"):
+        """Collective over the torch.distributed process group ``dist`` (any
+        backend): set up the expert-parallel exchange, 'peer' or 'nccl'."""
+        if mode == "peer":
+            blobs = [None] * self.ep_size
+            dist.all_gather_object(blobs, self.ep_peer_export())
+            self.ep_peer_enable(blobs)
+        else:
+            ids = [self.ep_unique_id() if self.ep_rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            self.ep_init(ids[0])
+
     # -- introspection ------------------------------------------------------
     def device_status(self) -> int:
         w = ctypes.c_int()

@@ -142,6 +142,20 @@ moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* 
 moe_b200_status moe_b200_ep_unique_id(char id_out[128]);
 moe_b200_status moe_b200_ep_init(moe_b200_handle h, const char id[128]);
 
+/* Peer-memory mode of the expert-parallel exchange (optional, instead of
+ * moe_b200_ep_init): the ranks map each other's exchange buffers (CUDA IPC over
+ * NVLink) and the exchange happens inside the permute kernel and the down
+ * GEMM's epilogue -- no NCCL call, no host wait.  Every rank calls
+ * moe_b200_ep_peer_export, the ranks exchange the blobs by any host channel, and
+ * every rank passes all of them, in rank order, to moe_b200_ep_peer_enable.  All
+ * ranks must be processes on one node whose GPUs have peer access.  (The
+ * reference enables peer access between all pairs at start-up too,
+ * src/getp/run.cpp:186-202.) */
+#define MOE_B200_EP_IPC_BYTES 64
+#define MOE_B200_EP_PEER_EXPORT_BYTES (4 * MOE_B200_EP_IPC_BYTES)
+moe_b200_status moe_b200_ep_peer_export(moe_b200_handle h, char* blob_out);
+moe_b200_status moe_b200_ep_peer_enable(moe_b200_handle h, const char* all_blobs);
+
 /* The host-side plan of one expert-parallel exchange, as moe_b200_forward
  * computes it: cnt_all [ep_size, n_experts] holds every rank's per-expert row
  * counts (rows are sent sorted by global expert); the outputs, each [ep_size],

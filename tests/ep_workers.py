@@ -129,10 +129,11 @@ def cpu_worker(rank, world, port, shape_kw, T, seed, outdir):
 
 
 # ---------------------------------------------------------------------------
-# GPU: the real thing, one process per GPU, NCCL inside the library.
+# GPU: the real thing, one process per GPU; the exchange inside the library
+# over NCCL (mode "nccl") or over peer memory (mode "peer").
 
 
-def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl):
+def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl, mode):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import gpt_oss_amd_b200 as pkg
     from gpt_oss_amd_b200 import synth
@@ -144,9 +145,7 @@ def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl):
     Tl = int(starts[rank + 1] - starts[rank])
     eng = pkg.MoEEngine(shape, max_tokens=max(int(np.diff(starts).max()), 1), ep_rank=rank,
                         ep_size=world, device=rank, gemm_impl=gemm_impl)
-    ids = [pkg.MoEEngine.ep_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(ids, src=0)
-    eng.ep_init(ids[0])
+    eng.ep_connect(dist, mode)
     lw = synth.make_layer(shape, seed, first=eng.first_expert, n=eng.n_local)
     eng.load_layer(0, lw)
     x_bits = synth.make_tokens(T, shape.hidden, seed)[starts[rank]:starts[rank + 1]]

@@ -5,8 +5,9 @@
   dispatch, regroup by local expert, return in the sender's order, combine --
   restated over gloo with the oracle computing the experts, against a
   single-process oracle run.
-* GPU (needs >= 2 devices): one process per GPU, NCCL all-to-all inside the
-  library, against the oracle and against the single-GPU run.
+* GPU (needs >= 2 devices): one process per GPU, the exchange inside the
+  library over NCCL and over peer memory, against the oracle and against the
+  single-GPU run.
 """
 import os
 import socket
@@ -51,8 +52,9 @@ def test_exchange_protocol_over_gloo(world):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
 @pytest.mark.parametrize("impl", [capi.GEMM_MMA_SYNC, capi.GEMM_TCGEN05])
-def test_expert_parallel_on_gpus(impl):
+def test_expert_parallel_on_gpus(impl, mode):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
@@ -60,7 +62,7 @@ def test_expert_parallel_on_gpus(impl):
     shape_kw = dict(hidden=256, intermediate=128, n_experts=16, top_k=4)
     shape = pkg.MoEShape(**shape_kw)
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(ep_workers.gpu_worker, args=(world, _free_port(), shape_kw, T, seed, d, impl),
+        mp.spawn(ep_workers.gpu_worker, args=(world, _free_port(), shape_kw, T, seed, d, impl, mode),
                  nprocs=world, join=True)
         parts = [dict(np.load(os.path.join(d, f"gpu_rank{r}.npz"))) for r in range(world)]
     assert all(int(p["status"]) == 0 for p in parts)
@@ -69,7 +71,7 @@ def test_expert_parallel_on_gpus(impl):
     x_bits = synth.make_tokens(T, shape.hidden, seed)
     ref = oracle_case(lw, x_bits)
     ref.pop("h")
-    m = compare(res, ref, shape.top_k, f"ep{world}")
+    m = compare(res, ref, shape.top_k, f"ep{world}-{mode}")
     print("ep", world, m)
     # every rank computed exactly its shard's rows
     hist = np.bincount(ref["topk_i"].reshape(-1), minlength=shape.n_experts)
