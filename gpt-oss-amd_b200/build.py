@@ -45,8 +45,8 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines: tuple = ()) -> str:
+    if not force and not defines and not _stale():
         return OUT
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.isfile(nvcc):
@@ -59,6 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "-Xlinker", f"-rpath={lib}",
         "-o", OUT,
     ]
+    cmd += [f"-D{d}" for d in defines]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
@@ -71,5 +72,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+          defines=tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D")))
     print(OUT)

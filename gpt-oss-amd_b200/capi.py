@@ -8,7 +8,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmoe_b200.so")
+LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(_HERE, "libmoe_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_NOT_LOADED, ERR_DEVICE, ERR_NCCL, ERR_UNSUPPORTED = range(8)
 DTYPE_F32, DTYPE_BF16 = 0, 1

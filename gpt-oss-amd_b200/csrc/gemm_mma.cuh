@@ -31,7 +31,8 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
 __device__ __forceinline__ float swiglu(float gate, float up, float alpha, float limit) {
     const float g = fminf(gate, limit);
     const float u = fminf(fmaxf(up, -limit), limit);
-    const float sig = 1.0f / (1.0f + __expf(-alpha * g));
+    // fast reciprocal: the IEEE division costs ~90 cycles per value in the epilogue
+    const float sig = __fdividef(1.0f, 1.0f + __expf(-alpha * g));
     return g * sig * (u + 1.0f);
 }
 

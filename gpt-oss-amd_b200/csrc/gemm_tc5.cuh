@@ -22,10 +22,12 @@
 //            arrivals and the TMA transaction bytes, ONE `empty` barrier per
 //            slot is signalled by tcgen05.commit, so the MMA-issuing thread does
 //            one wait and one commit per pipeline step.
-// The kernel is instantiated for BN = 64, 128 and 256 token rows per tile (see
-// Geo<BN> below).  Narrow tiles split the K loop over NACC accumulators in
-// tensor memory (summed in the epilogue): back-to-back MMAs into one
-// accumulator are a dependent chain whose latency bounds small-N tiles.
+// This is the kernel for LARGE batches (BN = 256 token rows per tile: a decoded
+// weight tile feeds 256 token rows, the best ratio of decode work to FLOPs that
+// two accumulator sets in tensor memory allow); calls with few rows per expert
+// use gemm_tc5_swap.cuh, where the token rows are on the TMEM lanes instead.  The
+// geometry stays a template (Geo<BN>): MT weight tiles per item and NACC K-split
+// accumulators are 1 here.
 //
 // Warp roles:
 //   warp 0       W producer        warp 1   B producer (TMA)
@@ -38,10 +40,8 @@
 // in the handle's status word, raises a CTA-wide abort flag and all roles fall
 // through to the common exit where tensor memory is released.
 #pragma once
-#include <cuda.h>
-
-#include "common.cuh"
 #include "gemm_mma.cuh"  // swiglu()
+#include "tc5_ptx.cuh"
 
 namespace moe {
 namespace tc5 {
@@ -50,7 +50,7 @@ constexpr int A_TILE_BYTES = TILE_M * 128;  // one decoded weight tile: 128 rows
 constexpr int MMA_WARP = 2;
 constexpr int DEQ_WARP0 = 3;
 constexpr int MAX_LOCAL_EXPERTS = 256;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr int EPI_STAGE_BYTES = 1024 + 64;  // per epilogue warp: 32 token rows x 16 features bf16, padded
 
 // Geometry per tile width BN (token rows per work item):
 //   MT      weight tiles (of 128 rows) per work item.  The activation tile is
@@ -73,14 +73,6 @@ template <>
 struct Geo<256> {
     static constexpr int MT = 1, G = 4, STAGES = 4, WS = 4, NACC = 1, SETS = 2;
 };
-template <>
-struct Geo<128> {
-    static constexpr int MT = 1, G = 4, STAGES = 4, WS = 12, NACC = 2, SETS = 2;
-};
-template <>
-struct Geo<64> {
-    static constexpr int MT = 1, G = 4, STAGES = 4, WS = 16, NACC = 4, SETS = 2;
-};
 
 template <int BN>
 __host__ __device__ constexpr int n_threads() {
@@ -93,204 +85,10 @@ __host__ __device__ constexpr int n_barriers() {
 template <int BN>
 __host__ __device__ constexpr int smem_bytes() {
     return Geo<BN>::STAGES * (Geo<BN>::MT * A_TILE_BYTES + BN * 128) +
-           Geo<BN>::WS * Geo<BN>::MT * CHUNK_BYTES + n_barriers<BN>() * 8 +
+           Geo<BN>::WS * Geo<BN>::MT * CHUNK_BYTES + 4 * Geo<BN>::MT * EPI_STAGE_BYTES +
+           n_barriers<BN>() * 8 +
            (MAX_LOCAL_EXPERTS + 1) * 3 * 4 + 64 + 1024;  // + tile tables + holder/flag + alignment slack
 }
-
-struct TensorMaps {
-    CUtensorMap box[4];  // token-row boxes of 32, 64, 128, 256 rows x 64 columns
-};
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done;
-}
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait.  Returns false when the time limit passed or another role has
-// raised the abort flag; the first to time out records `code`.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
-                                          volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity))
-        return true;
-    unsigned long long t_start = 0;
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity))
-            return true;
-        if ((it & 127u) == 0) {
-            if (*abort_flag)
-                return false;
-            const unsigned long long now = global_timer_ns();
-            if (t_start == 0)
-                t_start = now;
-            else if (now - t_start > WAIT_LIMIT_NS)
-                break;
-        }
-    }
-    report_status(status, code);
-    *abort_flag = 1;
-    return false;
-}
-
-// After an abort: give a copy that was already issued a bounded time to land
-// before the CTA exits.
-__device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
-    const unsigned long long t0 = global_timer_ns();
-    while (!mbar_try_wait(bar, parity)) {
-        if (global_timer_ns() - t0 > 100000000ull)  // 0.1 s
-            break;
-    }
-}
-
-__device__ __forceinline__ void fence_proxy_async_smem() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void fence_barrier_init() {
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
-                                          uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-                 "r"(ncols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-                 : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] . B[smem desc]^T, bf16 x bf16 -> fp32, issued by one thread.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Arrives on `bar` when every tcgen05.mma issued so far by this thread is done.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
-
-// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane
-// (taddr.lane + i), registers = columns.  No wait: pair with tmem_ld_wait().
-__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t r[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Sum over the NACC K-split accumulators (BN columns apart) of 32 columns.
-template <int NACC, int BN>
-__device__ __forceinline__ void tmem_ld_sum(uint32_t taddr, float v[32]) {
-    uint32_t r[32];
-    tmem_ld_32x32_issue(taddr, r);
-    tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 32; i++)
-        v[i] = __uint_as_float(r[i]);
-#pragma unroll
-    for (int a = 1; a < NACC; a++) {
-        tmem_ld_32x32_issue(taddr + (uint32_t)(a * BN), r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++)
-            v[i] += __uint_as_float(r[i]);
-    }
-}
-
-// Shared-memory matrix descriptor: K-major tile whose rows are 128 bytes
-// (64 bf16), 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
-    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for SW128 K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128.
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-    return (1u << 4)                       // D format fp32
-           | (1u << 7)                     // A format bf16
-           | (1u << 10)                    // B format bf16
-           | ((uint32_t)(n >> 3) << 17)    // N / 8
-           | ((uint32_t)(TILE_M >> 4) << 24);  // M / 16
-}
-
 
 struct TileInfo {
     int e, mt0, n_mt, row0, valid_n, n_mma, box_idx, box_rows;
@@ -335,14 +133,6 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, int m_ite
     return ti;
 }
 
-#define RING_ADVANCE(s, ph, depth) \
-    do {                           \
-        if (++(s) == (depth)) {    \
-            (s) = 0;               \
-            (ph) ^= 1u;            \
-        }                          \
-    } while (0)
-
 template <int MODE, int BN>
 __global__ void __launch_bounds__(n_threads<BN>(), 1)
 expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __restrict__ chunks,
@@ -375,7 +165,8 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
     unsigned char* a_ring = smem;
     unsigned char* b_ring = a_ring + STAGES * A_SLOT_BYTES;
     unsigned char* w_ring = b_ring + STAGES * B_SLOT_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(w_ring + WS * W_SLOT_BYTES);
+    unsigned char* epi_stage = w_ring + WS * W_SLOT_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
     int* s_tables = reinterpret_cast<int*>(bars + n_barriers<BN>());
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(s_tables + 3 * (MAX_LOCAL_EXPERTS + 1));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -479,28 +270,45 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ----------------------------
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            int it = 0;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-                const TileInfo ti = decode_tile<BN>(tile, m_tiles, m_items, tt, E);
-                const int set = it % SETS, round = it / SETS;
-                ok = mbar_wait(bar_tmem_empty(set), (uint32_t)(round & 1) ^ 1u, status,
-                               DS_TIMEOUT_TMEM_EMPTY, abort_flag);
-                if (!ok)
-                    break;
-                tc_fence_after();
-                const uint32_t d_set = tmem_base + (uint32_t)(set * SET_COLS);
-                const uint32_t idesc = make_idesc(ti.n_mma);
-                for (int ks = 0; ks < k_stages; ks++) {
+        // The whole warp runs the loop with no lane-divergent code but the elected
+        // issue itself: uniform control flow keeps the descriptors in uniform
+        // registers, where tcgen05.mma reads them from.  The barrier of the NEXT step
+        // is tested before the MMAs of this step are issued, so that its latency
+        // overlaps the issue instead of adding to the per-step chain of this warp.
+        // The operands in shared memory need no tcgen05 fence: TMA completes through
+        // the mbarrier and the decode warps fence the async proxy before they arrive.
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        int it = 0;
+        bool ready = false;  // full[s] already seen complete for phase ph
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            const TileInfo ti = decode_tile<BN>(tile, m_tiles, m_items, tt, E);
+            const int set = it % SETS, round = it / SETS;
+            ok = mbar_wait(bar_tmem_empty(set), (uint32_t)(round & 1) ^ 1u, status,
+                           DS_TIMEOUT_TMEM_EMPTY, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            tc_fence_after();  // the epilogue's tcgen05.ld of this set came before
+            const uint32_t d_set = tmem_base + (uint32_t)(set * SET_COLS);
+            const uint32_t idesc = make_idesc(ti.n_mma);
+            for (int ks = 0; ks < k_stages; ks++) {
+                if (!ready) {
                     ok = mbar_wait(bar_full(s), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok)
                         break;
-                    tc_fence_after();
-                    const uint64_t a_desc = make_sw128_desc(smem_u32(a_ring + s * A_SLOT_BYTES));
-                    const uint64_t b_desc = make_sw128_desc(smem_u32(b_ring + s * B_SLOT_BYTES));
+                }
+                if (lane == 0)
+                    TRACE(it * k_stages + ks, 4);
+                int s_next = s;
+                uint32_t ph_next = ph;
+                RING_ADVANCE(s_next, ph_next, STAGES);
+                const uint32_t peek = mbar_try_wait(bar_full(s_next), ph_next);
+                const uint64_t a_desc = make_sw128_desc(smem_u32(a_ring + s * A_SLOT_BYTES));
+                const uint64_t b_desc = make_sw128_desc(smem_u32(b_ring + s * B_SLOT_BYTES));
+                if (elect_one_sync()) {
 #pragma unroll
                     for (int j = 0; j < MT; j++) {
                         if (j < ti.n_mt) {
@@ -517,11 +325,16 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                         }
                     }
                     umma_commit(bar_empty(s));  // frees the slot when these MMAs have read it
-                    RING_ADVANCE(s, ph, STAGES);
                 }
-                if (ok)
-                    umma_commit(bar_tmem_full(set));
+                if (lane == 0)
+                    TRACE(it * k_stages + ks, 5);
+                ready = __all_sync(0xffffffffu, peek != 0);
+                s = s_next;
+                ph = ph_next;
             }
+            if (ok && elect_one_sync())
+                umma_commit(bar_tmem_full(set));
+            __syncwarp();
         }
     } else if (warp < EPI_WARP0) {
         // ------------------------------ MXFP4 decode --------------------------
@@ -633,6 +446,8 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
+            if (warp == EPI_WARP0 && lane == 0)
+                TRACE(it * k_stages, 10);
             tc_fence_after();
             if (j < ti.n_mt) {
                 const float* be = bias + (size_t)ti.e * bias_stride;
@@ -640,27 +455,44 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                 const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) +
                                         (uint32_t)(set * SET_COLS + j * NACC * BN);
                 if (MODE == 0) {
+                    // Lanes 2p / 2p+1 hold the gate / up row of feature pair p.  After one
+                    // exchange the even lane finishes columns c0..c0+15 of that feature and
+                    // the odd lane columns c0+16..c0+31.  The warp's 32 token rows x 16
+                    // features are transposed through shared memory so that every global
+                    // store writes 16 bytes per lane: 2-byte stores cost ~170 cycles per
+                    // warp instruction here, 16 of them per 32 columns.
                     uint16_t* h = static_cast<uint16_t*>(outp);
+                    unsigned char* stage = epi_stage + (warp - EPI_WARP0) * EPI_STAGE_BYTES;
+                    uint16_t* stage16 = reinterpret_cast<uint16_t*>(stage);
                     const float bm = be[m];  // 2I is a multiple of TILE_M: always in range
-                    const int jf = m >> 1;   // feature of this gate/up pair
+                    const int jf0 = ((ti.mt0 + j) * TILE_M + q * 32) >> 1;  // first of this warp's 16 features
                     const bool odd = (lane & 1) != 0;
+                    // token rows 16..31 sit 64 bytes further: no bank conflict between the halves
+                    const int st_idx = (odd ? 16 * 16 + 32 : 0) + (lane >> 1);
                     for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
                         float v[32];
                         tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
                         for (int c = 0; c < 16; c++) {
-                            // even lane = gate row, odd lane = the matching up row: the even
-                            // lane finishes columns c0+c, the odd lane columns c0+16+c
                             const float mine_lo = v[c] + bm, mine_hi = v[c + 16] + bm;
                             const float send = odd ? mine_lo : mine_hi;
                             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
                             const float gate = odd ? recv : mine_lo;
                             const float up = odd ? mine_hi : recv;
-                            const int col = c0 + c + (odd ? 16 : 0);
-                            if (col < ti.valid_n && jf < out_rows_valid)
-                                h[(size_t)(ti.row0 + col) * out_ld + jf] =
-                                    (uint16_t)float_to_bf16_bits(swiglu(gate, up, alpha, limit));
+                            stage16[st_idx + c * 16] =
+                                (uint16_t)float_to_bf16_bits(swiglu(gate, up, alpha, limit));
                         }
+                        __syncwarp();
+#pragma unroll
+                        for (int p = 0; p < 2; p++) {
+                            const int tok = (lane >> 1) + 16 * p, hf = lane & 1;
+                            const uint4 val = *reinterpret_cast<const uint4*>(
+                                stage + tok * 32 + hf * 16 + p * 64);
+                            const int col = c0 + tok, jf = jf0 + hf * 8;
+                            if (col < ti.valid_n && jf < out_rows_valid)
+                                *reinterpret_cast<uint4*>(h + (size_t)(ti.row0 + col) * out_ld + jf) = val;
+                        }
+                        __syncwarp();
                     }
                 } else {
                     float* y = static_cast<float*>(outp);
@@ -688,6 +520,8 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(bar_tmem_empty(set));
+            if (warp == EPI_WARP0 && lane == 0)
+                TRACE(it * k_stages, 11);
         }
     }
 

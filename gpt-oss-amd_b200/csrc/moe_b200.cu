@@ -14,6 +14,7 @@
 #include "ep.cuh"
 #include "gemm_mma.cuh"
 #include "gemm_tc5.cuh"
+#include "gemm_tc5_swap.cuh"
 #include "mxfp4.cuh"
 #include "plan.cuh"
 #include "route.cuh"
@@ -172,6 +173,9 @@ moe_b200_status check_layer(moe_b200_handle h, int layer) {
 // tokens per block) so that a decode-sized batch still spreads over the GPU.
 constexpr int ROUTE_SMALL_MAX_TOKENS = 2048;
 
+constexpr int TC5_BN = 256;                   // token rows per tile of the large-batch GEMM
+constexpr int SWAP_MAX_ROWS_PER_EXPERT = 96;  // at most this many rows per expert: small-batch GEMM
+
 int route_block_tokens(int T, int H) {
     return (T <= ROUTE_SMALL_MAX_TOKENS && route_small_smem_bytes(H) <= 200 * 1024) ? RBS : RB;
 }
@@ -212,20 +216,20 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
     return MOE_B200_OK;
 }
 
-template <int BN>
+// Large batches: weights on the TMEM lanes, 256 token rows per tile (gemm_tc5.cuh).
 moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
                            const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
                            const int* row_dst, float* const* row_ptr, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+    constexpr int BN = TC5_BN;
     constexpr int smem = tc5::smem_bytes<BN>();
-    constexpr int bit = BN == 64 ? 1 : BN == 128 ? 2 : 4;
-    if (!(h->smem_attr_done & bit)) {  // per handle: the attribute is per device
+    if (!(h->smem_attr_done & 1)) {  // per handle: the attribute is per device
         CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<0, BN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<1, BN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        h->smem_attr_done |= bit;
+        h->smem_attr_done |= 1;
     }
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
     tc5::expert_gemm_tc5_kernel<0, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
@@ -241,10 +245,40 @@ moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5:
     return MOE_B200_OK;
 }
 
+// Small batches: token rows on the TMEM lanes, 256 weight rows per tile (gemm_tc5_swap.cuh).
+moe_b200_status launch_swap(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
+                            const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
+                            const int* row_dst, float* const* row_ptr, cudaStream_t st) {
+    const moe_b200_config& c = h->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+    namespace sw = tc5::swp;
+    if (!(h->smem_attr_done & 2)) {
+        CU_TRY(h, cudaFuncSetAttribute(sw::expert_gemm_swap_kernel<0>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, sw::SMEM_BYTES));
+        CU_TRY(h, cudaFuncSetAttribute(sw::expert_gemm_swap_kernel<1>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, sw::SMEM_BYTES));
+        h->smem_attr_done |= 2;
+    }
+    prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
+    sw::expert_gemm_swap_kernel<0><<<h->n_sms, sw::N_THREADS, sw::SMEM_BYTES, st>>>(
+        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
+        EL, h->hbuf, I, I, nullptr, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+    prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
+    sw::expert_gemm_swap_kernel<1><<<h->n_sms, sw::N_THREADS, sw::SMEM_BYTES, st>>>(
+        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
+        EL, yout, H, H, row_dst, row_ptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    h->last_launches += 2;
+    return MOE_B200_OK;
+}
+
 // The two grouped GEMMs over `g_*` tables describing rows grouped by local
-// expert; `bn` is the n-tile width the tables were built for.
+// expert; `bn` is the number of token rows per tile the tables were built for
+// (pick_bn), which also selects the kernel.
 moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const uint16_t* xin,
-                             const tc5::TensorMaps& maps_x, int rows_upper, int bn, const int* g_off,
+                             const tc5::TensorMaps& maps_x, int rows_upper, int bn,
+                             const int* g_off,
                              const int* g_cnt, const int* g_tile_start, float* yout,
                              const int* row_dst, float* const* row_ptr, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
@@ -264,26 +298,27 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
                                                       row_dst, row_ptr, c.swiglu_alpha,
                                                       c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
-    } else if (bn == 64) {
-        return launch_tc5<64>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
-    } else if (bn == 128) {
-        return launch_tc5<128>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
+    } else if (bn == tc5::swp::BM) {
+        return launch_swap(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
+    } else if (bn == TC5_BN) {
+        return launch_tc5(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
     } else {
-        return launch_tc5<256>(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
+        return fail(h, MOE_B200_ERR_INVALID, "tile tables were built for another tile height");
     }
     h->last_launches += 2;
     return MOE_B200_OK;
 }
 
-// Token rows per GEMM n-tile for a call that has `rows` rows spread over the
-// local experts: a narrow tile (deeper weight and activation rings) when the
-// experts see few rows each and the call is bound by weight streaming, the
-// widest tile otherwise.  Any choice is correct for any distribution of rows.
+// Token rows per GEMM tile for a call that has `rows` rows spread over the local
+// experts; the tile tables are built for it and it selects the kernel: few rows per
+// expert (bound by weight streaming and by the MMA warp's per-step chain) -> token
+// rows on the TMEM lanes, 128 per tile; otherwise weights on the lanes and 256
+// token rows per tile.  Any choice is correct for any distribution of rows.
 int pick_bn(moe_b200_handle h, int rows) {
     if (h->cfg.gemm_impl == MOE_B200_GEMM_MMA_SYNC)
         return V0_BN;
     const int per_expert = rows / (h->n_local > 0 ? h->n_local : 1);
-    return per_expert <= 48 ? 64 : per_expert <= 96 ? 128 : 256;
+    return per_expert <= SWAP_MAX_ROWS_PER_EXPERT ? tc5::swp::BM : TC5_BN;
 }
 
 }  // namespace
@@ -970,3 +1005,12 @@ moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local
 }
 
 }  // extern "C"
+
+#ifdef TC5_TRACE
+// Debug builds only (not declared in the header): reads the hand-off timestamps.
+extern "C" int moe_b200_debug_trace_read(long long* out, int n) {
+    cudaDeviceSynchronize();
+    const size_t bytes = sizeof(long long) * (size_t)n;
+    return (int)cudaMemcpyFromSymbol(out, moe::tc5::g_trace, bytes);
+}
+#endif

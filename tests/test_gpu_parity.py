@@ -113,6 +113,7 @@ CASES = [
     (128, 64, 16, 8, 17),
     (128, 64, 32, 4, 2500),   # above the small-batch routing threshold
     (128, 64, 128, 4, 2100),
+    (320, 192, 4, 2, 700),    # large-batch GEMM kernel with partial weight tiles
 ]
 
 
