@@ -50,7 +50,7 @@ constexpr int A_TILE_BYTES = TILE_M * 128;  // one decoded weight tile: 128 rows
 constexpr int MMA_WARP = 2;
 constexpr int DEQ_WARP0 = 3;
 constexpr int MAX_LOCAL_EXPERTS = 256;
-constexpr int EPI_STAGE_BYTES = 1024 + 64;  // per epilogue warp: 32 token rows x 16 features bf16, padded
+constexpr int EPI_STAGE_BYTES = 2048;  // per epilogue warp: 32 token rows x 16 features bf16 (padded) or 16 token rows x 32 columns fp32
 
 // Geometry per tile width BN (token rows per work item):
 //   MT      weight tiles (of 128 rows) per work item.  The activation tile is
@@ -495,23 +495,43 @@ expert_gemm_tc5_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* _
                         __syncwarp();
                     }
                 } else {
+                    // A lane holds one output column m for 32 token rows; 16 token rows
+                    // at a time are transposed through shared memory so that a lane stores
+                    // 16 bytes and a warp instruction four whole 128-byte row segments
+                    // (a global store costs this kernel ~170 cycles per warp instruction
+                    // whatever its width: one per token row made the epilogue longer
+                    // than the main loop).
                     float* y = static_cast<float*>(outp);
-                    const bool m_ok = m < out_rows_valid;
-                    const float bm = m_ok ? be[m] : 0.f;
+                    unsigned char* stage = epi_stage + (warp - EPI_WARP0) * EPI_STAGE_BYTES;
+                    float* stage32 = reinterpret_cast<float*>(stage);
+                    const float bm = (m < out_rows_valid) ? be[m] : 0.f;
+                    const int m4 = (ti.mt0 + j) * TILE_M + q * 32 + (lane & 7) * 4;  // columns this lane stores
+                    const bool m4_ok = m4 < out_rows_valid;                          // the width is a multiple of 4
                     for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
                         float v[32];
                         tmem_ld_sum<NACC, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
-                        for (int c = 0; c < 32; c++) {
-                            const int col = c0 + c;
-                            if (col < ti.valid_n && m_ok) {
-                                // result row: on another GPU (peer mode), at a remapped row
-                                // (received order), or in place
-                                float* yrow = row_ptr ? row_ptr[ti.row0 + col]
-                                                      : y + (size_t)(row_dst ? row_dst[ti.row0 + col]
-                                                                             : (ti.row0 + col)) * out_ld;
-                                yrow[m] = v[c] + bm;
+                        for (int half = 0; half < 2; half++) {
+#pragma unroll
+                            for (int c = 0; c < 16; c++)
+                                stage32[c * 32 + lane] = v[half * 16 + c] + bm;
+                            __syncwarp();
+#pragma unroll
+                            for (int p = 0; p < 4; p++) {
+                                const int tok = (lane >> 3) + 4 * p;
+                                const float4 val =
+                                    *reinterpret_cast<const float4*>(stage + (lane + 32 * p) * 16);
+                                const int col = c0 + half * 16 + tok;
+                                if (col < ti.valid_n && m4_ok) {
+                                    // result row: on another GPU (peer mode), at a remapped row
+                                    // (received order), or in place
+                                    const int rr = ti.row0 + col;
+                                    float* yrow = row_ptr ? row_ptr[rr]
+                                                          : y + (size_t)(row_dst ? row_dst[rr] : rr) * out_ld;
+                                    *reinterpret_cast<float4*>(yrow + m4) = val;
+                                }
                             }
+                            __syncwarp();
                         }
                     }
                 }
