@@ -144,7 +144,7 @@ wait_counts_plan_kernel(int E, int G, int rank, int bn, Table tb, int seq, int* 
 
 // The permute kernel of plan.cuh with the destination on another GPU: stable
 // placement of every (token, k) assignment, row copied as bf16 into the owner's
-// expert-grouped buffer, return address beside it.  grid = routing blocks.
+// expert-grouped buffer, return address beside it.  grid = (routing blocks, S).
 __global__ void __launch_bounds__(256)
 permute_to_peers_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, int E, int G,
                         int rank, int rb, const int* __restrict__ topk_i,
@@ -168,7 +168,9 @@ permute_to_peers_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, 
         s_e[a] = e;
     }
     __syncthreads();
-    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
+    const int per = (n_assign + gridDim.y - 1) / gridDim.y;  // gridDim.y blocks share a routing block
+    const int a_lo = blockIdx.y * per, a_hi = min(n_assign, a_lo + per);
+    for (int a = a_lo + threadIdx.x; a < a_hi; a += blockDim.x) {
         const int e = s_e[a];
         int row = -1;
         if (e >= 0) {
@@ -187,7 +189,7 @@ permute_to_peers_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, 
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int vec_per_row = H / 8;
-    for (int a = warp; a < n_assign; a += nwarps) {
+    for (int a = a_lo + warp; a < a_hi; a += nwarps) {
         const int row = s_row[a];
         if (row < 0)
             continue;

@@ -309,6 +309,13 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
     return MOE_B200_OK;
 }
 
+// Blocks per routing block of the permute kernels: about four blocks per SM, at least
+// one row per warp.
+int permute_split(moe_b200_handle h, int nblk, int n_assign) {
+    const int want = (4 * h->n_sms + nblk - 1) / (nblk > 0 ? nblk : 1);
+    return std::max(1, std::min({want, 8, n_assign / 8}));
+}
+
 // Token rows per GEMM tile for a call that has `rows` rows spread over the local
 // experts; the tile tables are built for it and it selects the kernel: few rows per
 // expert (bound by weight streaming and by the MMA warp's per-step chain) -> token
@@ -612,7 +619,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     h->last_launches++;
     if (T > 0 && !peer_mode) {
         prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
-        permute_kernel<<<nblk, 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb,
+        permute_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb,
                                             h->topk_i, h->blk_base, h->slot_of, h->row_token, h->xs,
                                             h->status);
         prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
@@ -631,7 +638,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
         peer::wait_counts_plan_kernel<<<1, 256, 0, s>>>(E, G, rank, bn, es.table, seq, es.g_cnt, es.g_off,
                                                         es.g_tile_start, es.send_base, h->status);
         if (T > 0)
-            peer::permute_to_peers_kernel<<<nblk, 256, 0, s>>>(
+            peer::permute_to_peers_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(
                 t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, G, rank, rb, h->topk_i, h->blk_base,
                 h->off, es.send_base, es.table, h->slot_of, h->status);
         peer::barrier_kernel<<<1, 32, 0, s>>>(1, E, G, rank, es.table, seq, h->status);

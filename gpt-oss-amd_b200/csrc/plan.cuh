@@ -60,7 +60,10 @@ plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __re
 
 // Stable placement of every (token, k) assignment into its expert's row range
 // and the row gather x[token] -> xs[row] as bf16 (fp32 input is rounded here:
-// src/hip/BLAS.hip:32-40).  grid = routing blocks of RB tokens, 256 threads.
+// src/hip/BLAS.hip:32-40).  grid = (routing blocks of RB tokens, S): the S
+// blocks of a routing block split its assignments, so that a batch of a few
+// thousand tokens still puts several blocks on every SM (the copy is bound by
+// loads in flight, not by the arithmetic).
 __global__ void __launch_bounds__(256)
 permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, int E, int rb,
                const int* __restrict__ topk_i, const int* __restrict__ blk_base,
@@ -83,7 +86,9 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
         s_e[a] = e;
     }
     __syncthreads();
-    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
+    const int per = (n_assign + gridDim.y - 1) / gridDim.y;
+    const int a_lo = blockIdx.y * per, a_hi = min(n_assign, a_lo + per);
+    for (int a = a_lo + threadIdx.x; a < a_hi; a += blockDim.x) {
         const int e = s_e[a];
         int pos = -1;
         if (e >= 0) {
@@ -99,7 +104,7 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int vec_per_row = H / 8;  // 8 bf16 = 16 bytes
-    for (int a = warp; a < n_assign; a += nwarps) {
+    for (int a = a_lo + warp; a < a_hi; a += nwarps) {
         const int pos = s_pos[a];
         if (pos < 0)
             continue;
