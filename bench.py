@@ -145,7 +145,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="prefill120b", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "mma_sync"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "mma_sync", "tcgen05_1cta"])
     ap.add_argument("--cpu-sample", type=int, default=16, help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
@@ -211,7 +211,8 @@ def main():
         T_local = T_total
         scaling = "weak"
         tokens_per_step_job = T_total * world
-    gemm_impl = capi.GEMM_MMA_SYNC if args.impl == "mma_sync" else capi.GEMM_TCGEN05
+    gemm_impl = {"mma_sync": capi.GEMM_MMA_SYNC, "tcgen05_1cta": capi.GEMM_TCGEN05_1CTA}.get(
+        args.impl, capi.GEMM_TCGEN05)
     eng = pkg.MoEEngine(shape, n_layers=wl["L"], max_tokens=T_local, ep_rank=ep_rank, ep_size=ep,
                         device=local_rank, gemm_impl=gemm_impl)
     if ep > 1:

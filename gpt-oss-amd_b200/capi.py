@@ -12,7 +12,7 @@ LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(_HERE, "libmoe_b200.so
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_NOT_LOADED, ERR_DEVICE, ERR_NCCL, ERR_UNSUPPORTED = range(8)
 DTYPE_F32, DTYPE_BF16 = 0, 1
-GEMM_TCGEN05, GEMM_MMA_SYNC = 0, 1
+GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_TCGEN05_1CTA = 0, 1, 2
 EP_PEER_EXPORT_BYTES = 256
 
 #: every symbol include/moe_b200.h declares

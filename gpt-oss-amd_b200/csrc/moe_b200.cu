@@ -14,6 +14,7 @@
 #include "ep.cuh"
 #include "gemm_mma.cuh"
 #include "gemm_tc5.cuh"
+#include "gemm_tc5_pair.cuh"
 #include "gemm_tc5_swap.cuh"
 #include "mxfp4.cuh"
 #include "plan.cuh"
@@ -75,6 +76,7 @@ struct moe_b200_handle_s {
     uint8_t* stage_scales = nullptr;
 
     tc5::TensorMaps maps_x{}, maps_h{};  // TMA maps over the GEMM inputs
+    int pair_grid = 0;       // CTAs of the pair GEMM (2 x resident clusters)
     int smem_attr_done = 0;  // bit set: shared-memory opt-in of a kernel family done on this device
 
     ep::State ep;
@@ -245,6 +247,80 @@ moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5:
     return MOE_B200_OK;
 }
 
+// Large batches on CTA pairs (gemm_tc5_pair.cuh): cluster launch, one cluster per SM pair.
+template <int MODE>
+moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
+                                   const tc5::TensorMaps& maps, const uint8_t* chunks, size_t stride,
+                                   int ks, int m_tiles, const float* bias, int bias_stride,
+                                   const int* g_off, const int* g_cnt, const int* g_tile_start, int EL,
+                                   void* out, int out_ld, int out_valid, const int* row_dst,
+                                   float* const* row_ptr) {
+    namespace pr = tc5::pair;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(pr::N_THREADS);
+    cfg.dynamicSmemBytes = pr::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU_TRY(h, cudaLaunchKernelEx(&cfg, pr::expert_gemm_pair_kernel<MODE>, maps, chunks, stride, ks, m_tiles,
+                                 bias, bias_stride, g_off, g_cnt, g_tile_start, EL, out, out_ld, out_valid,
+                                 row_dst, row_ptr, h->cfg.swiglu_alpha, h->cfg.swiglu_limit, h->status));
+    return MOE_B200_OK;
+}
+
+moe_b200_status launch_pair(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
+                            const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
+                            const int* row_dst, float* const* row_ptr, cudaStream_t st) {
+    const moe_b200_config& c = h->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+    namespace pr = tc5::pair;
+    if (!(h->smem_attr_done & 4)) {
+        CU_TRY(h, cudaFuncSetAttribute(pr::expert_gemm_pair_kernel<0>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, pr::SMEM_BYTES));
+        CU_TRY(h, cudaFuncSetAttribute(pr::expert_gemm_pair_kernel<1>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, pr::SMEM_BYTES));
+        // clusters that can be resident at once: a persistent kernel must not launch more
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (h->n_sms / 2));
+        cfg.blockDim = dim3(pr::N_THREADS);
+        cfg.dynamicSmemBytes = pr::SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n_clusters = 0;
+        CU_TRY(h, cudaOccupancyMaxActiveClusters(&n_clusters, pr::expert_gemm_pair_kernel<0>, &cfg));
+        if (n_clusters < 1)
+            return fail(h, MOE_B200_ERR_CUDA, "no CTA pair of the expert GEMM fits on this device");
+        h->pair_grid = 2 * std::min(n_clusters, h->n_sms / 2);
+        h->smem_attr_done |= 4;
+    }
+    prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
+    moe_b200_status s1 = launch_pair_kernel<0>(h, h->pair_grid, st, maps_x, lw.w1, h->stride1, h->ks1,
+                                               h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
+                                               EL, h->hbuf, I, I, nullptr, nullptr);
+    if (s1)
+        return s1;
+    prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
+    s1 = launch_pair_kernel<1>(h, h->pair_grid, st, h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2,
+                               lw.bias2, H, g_off, g_cnt, g_tile_start, EL, yout, H, H, row_dst, row_ptr);
+    if (s1)
+        return s1;
+    prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    h->last_launches += 2;
+    return MOE_B200_OK;
+}
+
 // Small batches: token rows on the TMEM lanes, 256 weight rows per tile (gemm_tc5_swap.cuh).
 moe_b200_status launch_swap(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
                             const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
@@ -300,8 +376,10 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
         prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
     } else if (bn == tc5::swp::BM) {
         return launch_swap(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
-    } else if (bn == TC5_BN) {
+    } else if (bn == TC5_BN && c.gemm_impl == MOE_B200_GEMM_TCGEN05_1CTA) {
         return launch_tc5(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
+    } else if (bn == TC5_BN) {
+        return launch_pair(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
     } else {
         return fail(h, MOE_B200_ERR_INVALID, "tile tables were built for another tile height");
     }
@@ -369,7 +447,8 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         return fail(nullptr, MOE_B200_ERR_INVALID, "n_layers and max_tokens must be positive");
     if (c.ep_size <= 0 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.ep_size > c.n_experts)
         return fail(nullptr, MOE_B200_ERR_INVALID, "bad ep_rank / ep_size");
-    if (c.gemm_impl != MOE_B200_GEMM_TCGEN05 && c.gemm_impl != MOE_B200_GEMM_MMA_SYNC)
+    if (c.gemm_impl != MOE_B200_GEMM_TCGEN05 && c.gemm_impl != MOE_B200_GEMM_MMA_SYNC &&
+        c.gemm_impl != MOE_B200_GEMM_TCGEN05_1CTA)
         return fail(nullptr, MOE_B200_ERR_INVALID, "unknown gemm_impl");
 
     int n_dev = 0;
@@ -454,7 +533,7 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         if (st)
             return bail(st);
     }
-    if (c.gemm_impl == MOE_B200_GEMM_TCGEN05) {
+    if (c.gemm_impl != MOE_B200_GEMM_MMA_SYNC) {
         void* x_base = (c.ep_size > 1) ? (void*)h->ep.xgrp : (void*)h->xs;
         const int x_rows = (c.ep_size > 1) ? h->rows_cap : (int)TK;
         if ((st = make_maps(h, &h->maps_x, x_base, H, x_rows)) ||

@@ -53,10 +53,13 @@ typedef enum {
 #define MOE_B200_DTYPE_F32 0  /* the engine's s->t buffer (include/model.hpp:113) */
 #define MOE_B200_DTYPE_BF16 1 /* already-rounded activations                      */
 
-/* Expert GEMM implementations.  TCGEN05 is the product path; MMA_SYNC is a
- * plain warp-MMA kernel kept to cross-check it on the device. */
+/* Expert GEMM implementations.  TCGEN05 is the product path (large batches run
+ * on CTA pairs, tcgen05.mma.cta_group::2); MMA_SYNC is a plain warp-MMA kernel
+ * kept to cross-check it on the device; TCGEN05_1CTA runs large batches on the
+ * single-CTA tcgen05 kernel (for comparison). */
 #define MOE_B200_GEMM_TCGEN05 0
 #define MOE_B200_GEMM_MMA_SYNC 1
+#define MOE_B200_GEMM_TCGEN05_1CTA 2
 
 /* Mirrors the MoE-related fields of OssConfig (include/model.hpp:25-48) plus
  * the expert-parallel placement of OssTransformerHybrid (include/model.hpp:

@@ -17,7 +17,8 @@ from parity_util import compare, oracle_case, run_gpu
 
 pytestmark = pytest.mark.gpu
 
-IMPLS = [pytest.param(capi.GEMM_MMA_SYNC, id="mma_sync"), pytest.param(capi.GEMM_TCGEN05, id="tcgen05")]
+IMPLS = [pytest.param(capi.GEMM_MMA_SYNC, id="mma_sync"), pytest.param(capi.GEMM_TCGEN05, id="tcgen05"),
+         pytest.param(capi.GEMM_TCGEN05_1CTA, id="tcgen05_1cta")]
 
 
 def _bits(t):
