@@ -330,8 +330,14 @@ def main():
             + rows_local * I * 2  # packed W1 + scales + bias, rows in, h out
         achieved = alg / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None
         peak, unit = peaks["hbm_gbs"], "GB/s"
-    roofline = {"kernel": "expert_gemm_tc5_kernel<0> (gate/up GEMM + SwiGLU)" if gemm_impl == capi.GEMM_TCGEN05
-                else "expert_gemm_mma_kernel<0>",
+    # the library picks the kernel from the rows per local expert (pick_bn in csrc/moe_b200.cu)
+    small = (T_local * K) // max(eng.n_local, 1) <= 96
+    kernel = {capi.GEMM_MMA_SYNC: "expert_gemm_mma_kernel<0>",
+              capi.GEMM_TCGEN05_1CTA: "tc5::swp::expert_gemm_swap_kernel<0>" if small
+              else "tc5::expert_gemm_tc5_kernel<0,256>",
+              capi.GEMM_TCGEN05: "tc5::swp::expert_gemm_swap_kernel<0>" if small
+              else "tc5::pair::expert_gemm_pair_kernel<0>"}[gemm_impl]
+    roofline = {"kernel": kernel + " (gate/up GEMM + SwiGLU)",
                 "bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit,
                 "frac": (achieved / peak) if achieved else None, "peak_source": peaks["source"],
                 "traffic": NCU_TRAFFIC.get(args.workload), "launch_ms": g1_ms,
@@ -355,7 +361,8 @@ def main():
         config["ep_exchange"] = args.ep_exchange
     config.update({"parallelism": (f"ep{ep}" if ep > 1 else ("single" if world == 1 else f"replicas{world}")),
                    "tokens_per_rank": T_local, "experts_per_rank": eng.n_local,
-                   "gemm_impl": "tcgen05" if gemm_impl == capi.GEMM_TCGEN05 else "mma_sync",
+                   "gemm_impl": {capi.GEMM_TCGEN05: "tcgen05", capi.GEMM_MMA_SYNC: "mma_sync",
+                                 capi.GEMM_TCGEN05_1CTA: "tcgen05_1cta"}[gemm_impl],
                    "expert_rows_max_over_mean": (max(counts) / (sum(counts) / len(counts))) if sum(counts) else None})
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
