@@ -55,9 +55,9 @@ METRIC = "moe_layer_tokens_per_s"
 
 # DRAM traffic of one launch of the dominant kernel from an ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum), bytes; None until captured.
-NCU_TRAFFIC = {"prefill120b": 1.89e9,   # 2048-token capture scaled by components (see profiles/)
+NCU_TRAFFIC = {"prefill120b": 1.80e9,   # 2048-token capture scaled by components (see profiles/)
                "prefill20b_zipf": None,
-               "decode20b": 297.5e6,    # captured directly: one layer, 256 tokens
+               "decode20b": 296.3e6,    # captured directly: one layer, 256 tokens
                "layer20b": None}
 
 

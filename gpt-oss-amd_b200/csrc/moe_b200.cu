@@ -172,8 +172,11 @@ moe_b200_status check_layer(moe_b200_handle h, int layer) {
 }
 
 // Batches up to this many tokens are routed by the warp-per-token kernel (RBS
-// tokens per block) so that a decode-sized batch still spreads over the GPU.
-constexpr int ROUTE_SMALL_MAX_TOKENS = 2048;
+// tokens per block) so that a decode-sized batch still spreads over the GPU.  Its
+// time grows with the batch (35 us at 256 tokens, 138 us at 2048) while the
+// tensor-core kernel takes ~85 us for anything up to 64 tokens x 148 blocks: the
+// crossover is a little above 1024 tokens.
+constexpr int ROUTE_SMALL_MAX_TOKENS = 1024;
 
 constexpr int TC5_BN = 256;                   // token rows per tile of the large-batch GEMM
 constexpr int SWAP_MAX_ROWS_PER_EXPERT = 96;  // at most this many rows per expert: small-batch GEMM
