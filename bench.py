@@ -274,6 +274,18 @@ def main():
     for _ in range((n_prof + wl["L"] - 1) // wl["L"]):
         step()
     barrier()
+    # a short run can end before nvidia-smi has printed its first line: keep the same
+    # load on the GPU (untimed steps, the same number on every rank) until the whole
+    # sampled region is about a second long
+    done_ms = (warmup + 2 * args.steps) * (ms_total / args.steps)
+    extra = int(min(5000, max(0.0, 1000.0 - done_ms) / max(ms_total / args.steps, 1e-3)))
+    if dist is not None:
+        te = torch.tensor([extra], dtype=torch.int64, device="cuda")
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        extra = int(te[0])
+    for _ in range(extra):
+        step()
+    barrier()
     clocks = sampler.stop() if sampler else None
     stage_ms = {}
     for c in range(n_prof):
