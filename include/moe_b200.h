@@ -174,7 +174,10 @@ size_t moe_b200_device_bytes(moe_b200_handle h);
  * is NULL).  Never NULL. */
 const char* moe_b200_last_error(moe_b200_handle h);
 /* Reads the device status word (synchronises the device): 0 = no kernel has
- * reported a problem; otherwise a code naming the wait that ran out. */
+ * reported a problem; otherwise a code naming the wait that ran out (0x101..
+ * 0x106: a pipeline barrier of an expert GEMM; 0x201 / 0x202: a scale byte or
+ * expert index out of range; 0x301: a peer's flag in the peer-memory exchange,
+ * i.e. a rank that did not join the call within 2 s).  The context stays usable. */
 moe_b200_status moe_b200_device_status(moe_b200_handle h, int* status_word);
 /* Number of kernels the last moe_b200_forward launched on this handle. */
 int moe_b200_last_launch_count(moe_b200_handle h);

@@ -164,3 +164,35 @@ def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl, mode):
     dist.barrier()
     eng.close()
     dist.destroy_process_group()
+
+
+def gpu_missing_rank_worker(rank, world, port, shape_kw, T, seed, outdir):
+    """Failure detection without a GPU fault: rank 1 never joins the call.  Rank 0's
+    peer-flag waits run out (2 s each), its kernels return, the status word names the
+    wait and the context stays usable.  Rank 1 stays alive (its buffers stay mapped)
+    until rank 0 has read the status."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import gpt_oss_amd_b200 as pkg
+    from gpt_oss_amd_b200 import synth
+
+    _init(rank, world, port)
+    torch.cuda.set_device(rank)
+    shape = pkg.MoEShape(**shape_kw)
+    eng = pkg.MoEEngine(shape, max_tokens=T, ep_rank=rank, ep_size=world, device=rank)
+    eng.ep_connect(dist, "peer")
+    lw = synth.make_layer(shape, seed, first=eng.first_expert, n=eng.n_local)
+    eng.load_layer(0, lw)
+    dist.barrier()
+    status, usable = 0, True
+    if rank == 0:
+        x_bits = synth.make_tokens(T, shape.hidden, seed)
+        t = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).cuda().view(torch.bfloat16)
+        eng.forward(0, t)
+        torch.cuda.synchronize()
+        status = eng.device_status()
+        # the context still works
+        usable = bool((torch.ones(8, device="cuda") * 2).sum().item() == 16.0)
+    np.savez(os.path.join(outdir, f"miss_rank{rank}.npz"), status=status, usable=usable)
+    dist.barrier()  # rank 1 leaves only after rank 0 is done, nothing in flight
+    eng.close()
+    dist.destroy_process_group()

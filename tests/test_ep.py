@@ -87,3 +87,19 @@ def test_expert_parallel_on_gpus(impl, mode):
     d = single["out"].astype(np.float64) - res["out"].astype(np.float64)
     assert np.linalg.norm(d) / np.linalg.norm(single["out"].astype(np.float64)) <= 1e-4
     assert np.abs(d).max() <= 2e-3
+
+
+@pytest.mark.gpu
+def test_missing_rank_is_reported_not_hung():
+    """A rank that does not join an expert-parallel call: the host-made failure.  The
+    other rank's bounded flag waits run out, the status word says which wait, nothing
+    faults and the context stays usable."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    shape_kw = dict(hidden=128, intermediate=64, n_experts=8, top_k=2)
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(ep_workers.gpu_missing_rank_worker, args=(2, _free_port(), shape_kw, 40, 1, d),
+                 nprocs=2, join=True)
+        r0 = np.load(os.path.join(d, "miss_rank0.npz"))
+    assert int(r0["status"]) == 0x301  # DS_TIMEOUT_PEER (csrc/ep_peer.cuh)
+    assert bool(r0["usable"])
