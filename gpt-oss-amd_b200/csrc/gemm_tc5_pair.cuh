@@ -43,15 +43,9 @@ constexpr int A_SLOT_BYTES = TILE_M * 128;   // decoded weight tile: 128 rows x 
 constexpr int B_SLOT_BYTES = BNH * 128;      // half activation tile
 constexpr int MMA_WARP = 2;
 constexpr int DEQ_WARP0 = 3;
-#ifndef PAIR_G
-#define PAIR_G 4
-#define PAIR_SA 4
-#define PAIR_SB 8
-#define PAIR_NB 8
-#define PAIR_WS 4
-#endif
-constexpr int G = PAIR_G;                    // decode groups of four warps
-constexpr int SA = PAIR_SA, SB = PAIR_SB, NB = PAIR_NB, WS = PAIR_WS;
+constexpr int G = 4;                         // decode groups of four warps
+// A slots, B slots, barrier pairs, packed-weight slots (deeper W / B rings measured: no change)
+constexpr int SA = 4, SB = 8, NB = 8, WS = 4;
 constexpr int SETS = 2;
 constexpr int TMEM_COLS = SETS * BN;         // 512
 constexpr int EPI_WARP0 = DEQ_WARP0 + 4 * G;
