@@ -70,6 +70,8 @@ struct moe_b200_handle_s {
     void* t_dev = nullptr;
     float* out_dev = nullptr;
     cudaStream_t own_stream = nullptr;
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;  // host-buffer entry point: copies beside the compute
+    std::vector<cudaEvent_t> host_ev;                       // two per token chunk
 
     // upload staging (one expert matrix)
     uint8_t* stage_blocks = nullptr;
@@ -559,6 +561,12 @@ moe_b200_status moe_b200_destroy(moe_b200_handle h) {
         cudaEventDestroy(e);
     if (h->own_stream)
         cudaStreamDestroy(h->own_stream);
+    if (h->in_stream)
+        cudaStreamDestroy(h->in_stream);
+    if (h->out_stream)
+        cudaStreamDestroy(h->out_stream);
+    for (cudaEvent_t e : h->host_ev)
+        cudaEventDestroy(e);
     cudaGetLastError();
     delete h;
     return MOE_B200_OK;
@@ -793,20 +801,75 @@ moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* 
     const size_t H = h->cfg.hidden_dim, K = h->cfg.experts_per_token;
     const size_t esz = (t_dtype == MOE_B200_DTYPE_F32) ? 4 : 2;
     cudaStream_t s = h->own_stream;
-    if (n_tokens > 0)
-        CU_TRY(h, cudaMemcpyAsync(h->t_dev, t_host, (size_t)n_tokens * H * esz, cudaMemcpyHostToDevice, s));
-    st = moe_b200_forward(h, layer, h->t_dev, t_dtype, n_tokens, h->out_dev, 0, nullptr, nullptr,
-                          nullptr, reinterpret_cast<moe_b200_stream>(s));
-    if (st)
-        return st;
-    if (n_tokens > 0) {
-        CU_TRY(h, cudaMemcpyAsync(out_host, h->out_dev, (size_t)n_tokens * H * 4, cudaMemcpyDeviceToHost, s));
+    // The block is independent per token, and a row's result does not depend on which
+    // rows share its tile (the K loop has a fixed order), so a large batch is cut into
+    // token chunks whose host->device copy, compute and device->host copy overlap on
+    // three streams: the copies (PCIe, the fp32 result above all) take longer than the
+    // compute.  A chunk keeps >= 256 rows per expert so that the GEMM tiles stay full.
+    // Not with expert parallelism: every call is collective there and the ranks' token
+    // counts differ.
+    int chunk = n_tokens;
+    if (h->cfg.ep_size == 1) {
+        const int min_chunk = std::max(2048, (int)((256 * (size_t)h->cfg.n_experts + K - 1) / K));
+        if (n_tokens >= 2 * min_chunk) {
+            const int n_chunks = std::min(8, n_tokens / min_chunk);
+            chunk = ((n_tokens + n_chunks - 1) / n_chunks + 63) / 64 * 64;
+        }
+    }
+    if (chunk >= n_tokens) {
+        if (n_tokens > 0)
+            CU_TRY(h, cudaMemcpyAsync(h->t_dev, t_host, (size_t)n_tokens * H * esz, cudaMemcpyHostToDevice, s));
+        st = moe_b200_forward(h, layer, h->t_dev, t_dtype, n_tokens, h->out_dev, 0, nullptr, nullptr,
+                              nullptr, reinterpret_cast<moe_b200_stream>(s));
+        if (st)
+            return st;
+        if (n_tokens > 0) {
+            CU_TRY(h, cudaMemcpyAsync(out_host, h->out_dev, (size_t)n_tokens * H * 4, cudaMemcpyDeviceToHost, s));
+            if (topk_i_host)
+                CU_TRY(h, cudaMemcpyAsync(topk_i_host, h->topk_i, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
+            if (topk_w_host)
+                CU_TRY(h, cudaMemcpyAsync(topk_w_host, h->topk_w, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
+        }
+        CU_TRY(h, cudaStreamSynchronize(s));
+        return MOE_B200_OK;
+    }
+    const int n_chunks = (n_tokens + chunk - 1) / chunk;
+    if (!h->in_stream) {
+        CU_TRY(h, cudaStreamCreateWithFlags(&h->in_stream, cudaStreamNonBlocking));
+        CU_TRY(h, cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+    }
+    while ((int)h->host_ev.size() < 2 * n_chunks) {
+        cudaEvent_t e;
+        CU_TRY(h, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        h->host_ev.push_back(e);
+    }
+    const char* t_src = static_cast<const char*>(t_host);
+    char* t_dst = static_cast<char*>(h->t_dev);
+    for (int c = 0; c < n_chunks; c++) {
+        const size_t t0 = (size_t)c * chunk, n = std::min((size_t)chunk, (size_t)n_tokens - t0);
+        CU_TRY(h, cudaMemcpyAsync(t_dst + t0 * H * esz, t_src + t0 * H * esz, n * H * esz,
+                                  cudaMemcpyHostToDevice, h->in_stream));
+        CU_TRY(h, cudaEventRecord(h->host_ev[2 * c], h->in_stream));
+    }
+    for (int c = 0; c < n_chunks; c++) {
+        const size_t t0 = (size_t)c * chunk, n = std::min((size_t)chunk, (size_t)n_tokens - t0);
+        CU_TRY(h, cudaStreamWaitEvent(s, h->host_ev[2 * c], 0));
+        st = moe_b200_forward(h, layer, t_dst + t0 * H * esz, t_dtype, (int)n, h->out_dev + t0 * H, 0, nullptr,
+                              nullptr, nullptr, reinterpret_cast<moe_b200_stream>(s));
+        if (st)
+            return st;
+        // the routing side outputs live in the workspace the next chunk reuses: copy them here
         if (topk_i_host)
-            CU_TRY(h, cudaMemcpyAsync(topk_i_host, h->topk_i, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
+            CU_TRY(h, cudaMemcpyAsync(topk_i_host + t0 * K, h->topk_i, n * K * 4, cudaMemcpyDeviceToHost, s));
         if (topk_w_host)
-            CU_TRY(h, cudaMemcpyAsync(topk_w_host, h->topk_w, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
+            CU_TRY(h, cudaMemcpyAsync(topk_w_host + t0 * K, h->topk_w, n * K * 4, cudaMemcpyDeviceToHost, s));
+        CU_TRY(h, cudaEventRecord(h->host_ev[2 * c + 1], s));
+        CU_TRY(h, cudaStreamWaitEvent(h->out_stream, h->host_ev[2 * c + 1], 0));
+        CU_TRY(h, cudaMemcpyAsync(out_host + t0 * H, h->out_dev + t0 * H, n * H * 4, cudaMemcpyDeviceToHost,
+                                  h->out_stream));
     }
     CU_TRY(h, cudaStreamSynchronize(s));
+    CU_TRY(h, cudaStreamSynchronize(h->out_stream));
     return MOE_B200_OK;
 }
 

@@ -229,6 +229,24 @@ def test_forward_host_matches_device_path():
         assert torch.equal(out, dev)
 
 
+def test_forward_host_chunked_equals_device_path():
+    """Large batches go through the host-buffer entry point in token chunks whose
+    copies overlap the compute: same bits as one call on device buffers."""
+    shape = pkg.MoEShape(hidden=128, intermediate=64, n_experts=8, top_k=4)
+    lw = synth.make_layer(shape, seed=4)
+    T = 5000  # two chunks of 2560 tokens
+    x_bits = synth.make_tokens(T, 128, seed=4)
+    with pkg.MoEEngine(shape, max_tokens=T) as eng:
+        eng.load_layer(0, lw)
+        t = torch.from_numpy(x_bits.view(np.int16)).view(torch.bfloat16)
+        dev, _, ti, tw = eng.forward(0, t.cuda(), side=True)
+        dev, ti, tw = dev.cpu(), ti.cpu(), tw.cpu()
+        out = torch.empty(T, 128, dtype=torch.float32).pin_memory()
+        eng.forward_host(0, t.pin_memory(), out)
+        assert torch.equal(out, dev)
+        assert eng.device_status() == 0
+
+
 def test_router_indices_at_full_width_large_batch():
     """The tensor-core router (batches above the small-batch threshold) at the
     real hidden size and 128 experts: indices against the CPU engine's
