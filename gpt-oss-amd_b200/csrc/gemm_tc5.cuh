@@ -22,12 +22,14 @@
 //            arrivals and the TMA transaction bytes, ONE `empty` barrier per
 //            slot is signalled by tcgen05.commit, so the MMA-issuing thread does
 //            one wait and one commit per pipeline step.
-// This is the kernel for LARGE batches (BN = 256 token rows per tile: a decoded
-// weight tile feeds 256 token rows, the best ratio of decode work to FLOPs that
-// two accumulator sets in tensor memory allow); calls with few rows per expert
-// use gemm_tc5_swap.cuh, where the token rows are on the TMEM lanes instead.  The
-// geometry stays a template (Geo<BN>): MT weight tiles per item and NACC K-split
-// accumulators are 1 here.
+// This is the single-CTA kernel for LARGE batches (BN = 256 token rows per tile:
+// a decoded weight tile feeds 256 token rows, the best ratio of decode work to
+// FLOPs that two accumulator sets in tensor memory allow), selected with
+// gemm_impl = MOE_B200_GEMM_TCGEN05_1CTA; the default runs large batches on CTA
+// pairs (gemm_tc5_pair.cuh, same structure, half the activation bytes per SM) and
+// calls with few rows per expert on gemm_tc5_swap.cuh, where the token rows are on
+// the TMEM lanes instead.  The geometry stays a template (Geo<BN>): MT weight
+// tiles per item and NACC K-split accumulators are 1 here.
 //
 // Warp roles:
 //   warp 0       W producer        warp 1   B producer (TMA)
