@@ -9,10 +9,13 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(_HERE, "libmoe_b200.so")
+#: the same sources compiled with -DMOE_B200_TEST_AIDS (adds the cross-check GEMM); tests only
+TEST_AIDS_LIB_PATH = os.path.join(_HERE, "libmoe_b200_testaids.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NO_DEVICE, ERR_NOT_LOADED, ERR_DEVICE, ERR_NCCL, ERR_UNSUPPORTED = range(8)
 DTYPE_F32, DTYPE_BF16 = 0, 1
-GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_TCGEN05_1CTA = 0, 1, 2
+GEMM_TCGEN05 = 0
+GEMM_MMA_SYNC = 1  # exists in the test-aids build only
 EP_PEER_EXPORT_BYTES = 256
 
 #: every symbol include/moe_b200.h declares
@@ -24,11 +27,12 @@ SYMBOLS = [
     "moe_b200_last_expert_counts", "moe_b200_mxfp4_unpack", "moe_b200_unpack_resident",
     "moe_b200_version", "moe_b200_profile", "moe_b200_profile_read",
     "moe_b200_last_intermediate", "moe_b200_route_noalloc",
-    "moe_b200_ep_peer_export", "moe_b200_ep_peer_enable",
+    "moe_b200_ep_peer_export", "moe_b200_ep_peer_enable", "moe_b200_ep_peer_sequence",
+    "moe_b200_ep_peer_resync",
 ]
-N_STAGES = 9
+N_STAGES = 11
 STAGE_NAMES = ["route", "plan", "permute", "dispatch", "regroup", "gemm1", "gemm2", "return",
-               "combine"]
+               "combine", "h2d", "d2h"]
 
 
 class Config(ctypes.Structure):
@@ -48,56 +52,62 @@ class MoEError(RuntimeError):
         self.status = status
 
 
-_lib = None
+_libs = {}
 
 
-def lib() -> ctypes.CDLL:
-    """The loaded library.  Raises if it has not been built: nothing here falls
-    back to another implementation."""
-    global _lib
-    if _lib is None:
-        if not os.path.isfile(LIB_PATH):
+def _bind(L: ctypes.CDLL) -> ctypes.CDLL:
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    ip = ctypes.POINTER(ctypes.c_int)
+    L.moe_b200_shard_range.argtypes = [ci, ci, ci, ip, ip]
+    L.moe_b200_shard_range.restype = None
+    L.moe_b200_create.argtypes = [ctypes.POINTER(Config), ctypes.POINTER(vp)]
+    L.moe_b200_destroy.argtypes = [vp]
+    L.moe_b200_set_router.argtypes = [vp, ci, vp, vp]
+    L.moe_b200_set_experts_mxfp4.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp, vp, vp]
+    L.moe_b200_forward.argtypes = [vp, ci, vp, ci, ci, vp, ci, vp, vp, vp, vp]
+    L.moe_b200_forward_host.argtypes = [vp, ci, vp, ci, ci, vp, vp, vp]
+    L.moe_b200_ep_unique_id.argtypes = [ctypes.c_char_p]
+    L.moe_b200_ep_init.argtypes = [vp, ctypes.c_char_p]
+    L.moe_b200_ep_plan.argtypes = [ci, ci, ci, ip, ip, ip, ip, ip]
+    L.moe_b200_ep_plan.restype = None
+    L.moe_b200_device_bytes.argtypes = [vp]
+    L.moe_b200_device_bytes.restype = ctypes.c_size_t
+    L.moe_b200_last_error.argtypes = [vp]
+    L.moe_b200_last_error.restype = ctypes.c_char_p
+    L.moe_b200_device_status.argtypes = [vp, ip]
+    L.moe_b200_last_launch_count.argtypes = [vp]
+    L.moe_b200_last_expert_counts.argtypes = [vp, ip]
+    L.moe_b200_mxfp4_unpack.argtypes = [vp, vp, ctypes.c_longlong, ci, vp, vp]
+    L.moe_b200_unpack_resident.argtypes = [vp, ci, ci, ci, vp, vp]
+    L.moe_b200_version.restype = ctypes.c_char_p
+    L.moe_b200_last_intermediate.argtypes = [vp, ci, vp, vp]
+    L.moe_b200_route_noalloc.argtypes = [vp, ci, ci, ci, vp, vp, ci, ci, vp, vp, vp, vp, vp]
+    L.moe_b200_ep_peer_export.argtypes = [vp, ctypes.c_char_p]
+    L.moe_b200_ep_peer_enable.argtypes = [vp, ctypes.c_char_p]
+    L.moe_b200_ep_peer_sequence.argtypes = [vp]
+    L.moe_b200_ep_peer_resync.argtypes = [vp, ci]
+    L.moe_b200_profile.argtypes = [vp, ci]
+    L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
+    return L
+
+
+def lib(test_aids: bool = False) -> ctypes.CDLL:
+    """The loaded library (``test_aids``: the variant with the cross-check GEMM,
+    for tests).  Raises if it has not been built: nothing here falls back to
+    another implementation."""
+    path = TEST_AIDS_LIB_PATH if test_aids else LIB_PATH
+    if path not in _libs:
+        if not os.path.isfile(path):
             raise FileNotFoundError(
-                f"{LIB_PATH} is missing: build it with `python gpt-oss-amd_b200/build.py` "
+                f"{path} is missing: build it with `python gpt-oss-amd_b200/build.py` "
                 "(needs nvcc); there is no fallback implementation")
-        L = ctypes.CDLL(LIB_PATH)
-        vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
-        ip = ctypes.POINTER(ctypes.c_int)
-        L.moe_b200_shard_range.argtypes = [ci, ci, ci, ip, ip]
-        L.moe_b200_shard_range.restype = None
-        L.moe_b200_create.argtypes = [ctypes.POINTER(Config), ctypes.POINTER(vp)]
-        L.moe_b200_destroy.argtypes = [vp]
-        L.moe_b200_set_router.argtypes = [vp, ci, vp, vp]
-        L.moe_b200_set_experts_mxfp4.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp, vp, vp]
-        L.moe_b200_forward.argtypes = [vp, ci, vp, ci, ci, vp, ci, vp, vp, vp, vp]
-        L.moe_b200_forward_host.argtypes = [vp, ci, vp, ci, ci, vp, vp, vp]
-        L.moe_b200_ep_unique_id.argtypes = [ctypes.c_char_p]
-        L.moe_b200_ep_init.argtypes = [vp, ctypes.c_char_p]
-        L.moe_b200_ep_plan.argtypes = [ci, ci, ci, ip, ip, ip, ip, ip]
-        L.moe_b200_ep_plan.restype = None
-        L.moe_b200_device_bytes.argtypes = [vp]
-        L.moe_b200_device_bytes.restype = ctypes.c_size_t
-        L.moe_b200_last_error.argtypes = [vp]
-        L.moe_b200_last_error.restype = ctypes.c_char_p
-        L.moe_b200_device_status.argtypes = [vp, ip]
-        L.moe_b200_last_launch_count.argtypes = [vp]
-        L.moe_b200_last_expert_counts.argtypes = [vp, ip]
-        L.moe_b200_mxfp4_unpack.argtypes = [vp, vp, ctypes.c_longlong, ci, vp, vp]
-        L.moe_b200_unpack_resident.argtypes = [vp, ci, ci, ci, vp, vp]
-        L.moe_b200_version.restype = ctypes.c_char_p
-        L.moe_b200_last_intermediate.argtypes = [vp, ci, vp, vp]
-        L.moe_b200_route_noalloc.argtypes = [vp, ci, ci, ci, vp, vp, ci, ci, vp, vp, vp, vp, vp]
-        L.moe_b200_ep_peer_export.argtypes = [vp, ctypes.c_char_p]
-        L.moe_b200_ep_peer_enable.argtypes = [vp, ctypes.c_char_p]
-        L.moe_b200_profile.argtypes = [vp, ci]
-        L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
-        _lib = L
-    return _lib
+        _libs[path] = _bind(ctypes.CDLL(path))
+    return _libs[path]
 
 
-def check(status: int, handle=None) -> None:
+def check(status: int, handle=None, L: ctypes.CDLL | None = None) -> None:
     if status != OK:
-        text = lib().moe_b200_last_error(handle).decode("utf-8", "replace")
+        text = (L or lib()).moe_b200_last_error(handle).decode("utf-8", "replace")
         raise MoEError(status, text)
 
 

@@ -42,7 +42,7 @@ enum DeviceStatus : int {
     DS_TIMEOUT_EMPTY = 0x104,     // producer waiting for a free stage
     DS_TIMEOUT_TMEM_FULL = 0x105, // epilogue waiting for the accumulator
     DS_TIMEOUT_TMEM_EMPTY = 0x106,// MMA warp waiting for a drained accumulator
-    DS_BAD_SCALE = 0x201,         // a scale byte above MAX_SCALE_BYTE was uploaded
+    DS_BAD_SCALE = 0x201,         // a scale byte above MAX_SCALE_BYTE was uploaded (own flag word)
     DS_BAD_EXPERT = 0x202,        // router produced an expert index out of range
 };
 
@@ -137,5 +137,15 @@ __host__ __device__ __forceinline__ uint32_t mxfp4_decode_exact(uint32_t code, u
 }
 
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Clamped SwiGLU (src/run.cpp:673-689, src/hip/moe.hip:186-191): the gate has no
+// lower clamp.
+__device__ __forceinline__ float swiglu(float gate, float up, float alpha, float limit) {
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    // fast reciprocal: the IEEE division costs ~90 cycles per value in the epilogue
+    const float sig = __fdividef(1.0f, 1.0f + __expf(-alpha * g));
+    return g * sig * (u + 1.0f);
+}
 
 }  // namespace moe

@@ -47,8 +47,10 @@ struct State {
     char* arena = nullptr;        // one allocation holding xgrp, yrecv, ctrl, ret (peer-visible)
     size_t arena_off[4] = {0, 0, 0, 0};
     int2* ret = nullptr;          // [rows_cap] return address of each received row
-    float** row_ptr = nullptr;    // [rows_cap] owner's result row for each row computed here
-    int* send_base = nullptr;     // [E] where this rank's rows of expert e start at the owner
+    int* tickets = nullptr;       // [2] finished-block counters (permute kernel, down GEMM)
+    size_t arena_bytes = 0;
+    int rows_cap = 0;
+    bool nccl_buffers = false;    // xrecv / ysend / gather_src exist (NCCL mode only)
     peer::Table table{};
     std::vector<void*> opened;    // cudaIpcOpenMemHandle mappings to close
     bool peer_enabled = false;
@@ -182,28 +184,42 @@ inline int allocate(State& s, const moe_b200_config& c, int n_local, int first, 
     s.arena_off[1] = s.arena_off[0] + up((size_t)rows_cap * H * sizeof(uint16_t));  // yrecv
     s.arena_off[2] = s.arena_off[1] + up(TK * H * sizeof(float));            // ctrl
     s.arena_off[3] = s.arena_off[2] + up((G * E + 3 * G + 16) * sizeof(int));  // ret
-    const size_t arena_bytes = s.arena_off[3] + up((size_t)rows_cap * sizeof(int2));
-    if ((st = ep_alloc(&s.arena, arena_bytes, allocs, bytes, err)))
+    s.arena_bytes = s.arena_off[3] + up((size_t)rows_cap * sizeof(int2));
+    s.rows_cap = rows_cap;
+    if ((st = ep_alloc(&s.arena, s.arena_bytes, allocs, bytes, err)))
         return st;
     s.xgrp = reinterpret_cast<uint16_t*>(s.arena + s.arena_off[0]);
     s.yrecv = reinterpret_cast<float*>(s.arena + s.arena_off[1]);
     s.ctrl = reinterpret_cast<int*>(s.arena + s.arena_off[2]);
     s.ret = reinterpret_cast<int2*>(s.arena + s.arena_off[3]);
-    if ((st = ep_alloc(&s.row_ptr, (size_t)rows_cap, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.send_base, E, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.xrecv, (size_t)rows_cap * H, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.ysend, (size_t)rows_cap * H, allocs, bytes, err)) ||
+    if ((st = ep_alloc(&s.tickets, 2, allocs, bytes, err)) ||
         (st = ep_alloc(&s.g_cnt, n_local, allocs, bytes, err)) ||
         (st = ep_alloc(&s.g_off, n_local + 1, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.g_tile_start, n_local + 1, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.gather_src, rows_cap, allocs, bytes, err)) ||
-        (st = ep_alloc(&s.recv_off_dev, G, allocs, bytes, err)))
+        (st = ep_alloc(&s.g_tile_start, n_local + 1, allocs, bytes, err)))
         return st;
     s.cnt_all = s.ctrl;
-    if (cudaMemset(s.ctrl, 0, (G * E + 3 * G + 16) * sizeof(int)) != cudaSuccess) {
+    if (cudaMemset(s.ctrl, 0, (G * E + 3 * G + 16) * sizeof(int)) != cudaSuccess ||
+        cudaMemset(s.tickets, 0, 2 * sizeof(int)) != cudaSuccess) {
         err = "cudaMemset failed";
         return MOE_B200_ERR_CUDA;
     }
+    return 0;
+}
+
+// The buffers only the NCCL exchange uses (received rows in source order, results in
+// the same order, the regroup index): allocated by moe_b200_ep_init, so that a handle
+// in peer-memory mode does not carry them.
+inline int allocate_nccl(State& s, const moe_b200_config& c, std::vector<void*>& allocs, size_t& bytes,
+                         std::string& err) {
+    if (s.nccl_buffers)
+        return 0;
+    const size_t H = c.hidden_dim, E = c.n_experts, G = c.ep_size;
+    int st;
+    if ((st = ep_alloc(&s.xrecv, (size_t)s.rows_cap * H, allocs, bytes, err)) ||
+        (st = ep_alloc(&s.ysend, (size_t)s.rows_cap * H, allocs, bytes, err)) ||
+        (st = ep_alloc(&s.gather_src, s.rows_cap, allocs, bytes, err)) ||
+        (st = ep_alloc(&s.recv_off_dev, G, allocs, bytes, err)))
+        return st;
     if (cudaMallocHost(reinterpret_cast<void**>(&s.h_cnt_all), G * E * sizeof(int)) != cudaSuccess) {
         err = "cudaMallocHost failed";
         return MOE_B200_ERR_CUDA;
@@ -212,6 +228,7 @@ inline int allocate(State& s, const moe_b200_config& c, int n_local, int first, 
     s.send_off.assign(G, 0);
     s.recv_cnt.assign(G, 0);
     s.recv_off.assign(G, 0);
+    s.nccl_buffers = true;
     return 0;
 }
 
@@ -348,21 +365,49 @@ inline int exchange_and_compute(State& s, const moe_b200_config& c, int n_local,
 constexpr int PEER_BUFFERS = 4;  // xgrp, yrecv, ctrl, ret
 static_assert(sizeof(cudaIpcMemHandle_t) == MOE_B200_EP_IPC_BYTES, "IPC handle size");
 
-// blob: the arena's IPC handle, then the four byte offsets (xgrp, yrecv, ctrl, ret) as u64.
-inline int peer_export(State& s, char* out, std::string& err) {
+// What follows the IPC handle in an export blob.  Peers store into the arena at
+// addresses computed from THEIR configuration, so every field must agree between
+// the ranks before any mapping is used.
+struct PeerBlobInfo {
+    unsigned long long off[PEER_BUFFERS];  // byte offsets of xgrp, yrecv, ctrl, ret
+    unsigned long long arena_bytes;
+    int hidden, n_experts, top_k, max_tokens, rows_cap, ep_size, ep_rank, version;
+};
+constexpr int PEER_BLOB_VERSION = 2;
+static_assert(sizeof(cudaIpcMemHandle_t) + sizeof(PeerBlobInfo) <= MOE_B200_EP_PEER_EXPORT_BYTES,
+              "export blob size");
+
+inline PeerBlobInfo peer_blob_info(const State& s, const moe_b200_config& c) {
+    PeerBlobInfo b{};
+    for (int i = 0; i < PEER_BUFFERS; i++)
+        b.off[i] = s.arena_off[i];
+    b.arena_bytes = s.arena_bytes;
+    b.hidden = c.hidden_dim;
+    b.n_experts = c.n_experts;
+    b.top_k = c.experts_per_token;
+    b.max_tokens = c.max_tokens;
+    b.rows_cap = s.rows_cap;
+    b.ep_size = c.ep_size;
+    b.ep_rank = c.ep_rank;
+    b.version = PEER_BLOB_VERSION;
+    return b;
+}
+
+// blob: the arena's IPC handle, then PeerBlobInfo.
+inline int peer_export(State& s, const moe_b200_config& c, char* out, std::string& err) {
     memset(out, 0, MOE_B200_EP_PEER_EXPORT_BYTES);
     cudaIpcMemHandle_t h;
-    static_assert(sizeof(h) == MOE_B200_EP_IPC_BYTES, "cudaIpcMemHandle_t is expected to be 64 bytes");
     EP_CUDA(cudaIpcGetMemHandle(&h, s.arena));
     memcpy(out, &h, sizeof(h));
-    unsigned long long off[PEER_BUFFERS];
-    for (int i = 0; i < PEER_BUFFERS; i++)
-        off[i] = s.arena_off[i];
-    memcpy(out + sizeof(h), off, sizeof(off));
+    const PeerBlobInfo b = peer_blob_info(s, c);
+    memcpy(out + sizeof(h), &b, sizeof(b));
     return 0;
 }
 
 // all: [G][MOE_B200_EP_PEER_EXPORT_BYTES], the exports of every rank in rank order.
+// Every blob is checked against this rank's own configuration BEFORE any peer
+// memory is mapped: a rank created with other sizes would receive stores past the
+// end of its buffers.
 inline int peer_enable(State& s, const moe_b200_config& c, const char* all, std::string& err) {
     const int G = c.ep_size, rank = c.ep_rank;
     if (G > peer::MAX_RANKS) {
@@ -375,10 +420,37 @@ inline int peer_enable(State& s, const moe_b200_config& c, const char* all, std:
     }
     if (s.peer_enabled)
         return 0;
+    const PeerBlobInfo mine = peer_blob_info(s, c);
+    for (int p = 0; p < G; p++) {
+        PeerBlobInfo b;
+        memcpy(&b, all + (size_t)p * MOE_B200_EP_PEER_EXPORT_BYTES + MOE_B200_EP_IPC_BYTES, sizeof(b));
+        const char* what = nullptr;
+        if (b.version != PEER_BLOB_VERSION)
+            what = "blob version";
+        else if (b.ep_rank != p)
+            what = "rank order of the blobs";
+        else if (b.ep_size != mine.ep_size)
+            what = "ep_size";
+        else if (b.hidden != mine.hidden)
+            what = "hidden_dim";
+        else if (b.n_experts != mine.n_experts)
+            what = "n_experts";
+        else if (b.top_k != mine.top_k)
+            what = "experts_per_token";
+        else if (b.max_tokens != mine.max_tokens)
+            what = "max_tokens";
+        else if (b.rows_cap != mine.rows_cap || b.arena_bytes != mine.arena_bytes ||
+                 memcmp(b.off, mine.off, sizeof(b.off)) != 0)
+            what = "exchange buffer layout";
+        if (what) {
+            err = std::string("peer export of rank ") + std::to_string(p) + " does not match this rank: " +
+                  what + " differs (every rank must be created with the same hidden_dim, n_experts, "
+                         "experts_per_token, max_tokens and ep_size)";
+            return MOE_B200_ERR_INVALID;
+        }
+    }
     for (int p = 0; p < G; p++) {
         const char* blob = all + (size_t)p * MOE_B200_EP_PEER_EXPORT_BYTES;
-        unsigned long long off[PEER_BUFFERS];
-        memcpy(off, blob + MOE_B200_EP_IPC_BYTES, sizeof(off));
         char* base = s.arena;
         if (p != rank) {
             cudaIpcMemHandle_t h;
@@ -387,17 +459,11 @@ inline int peer_enable(State& s, const moe_b200_config& c, const char* all, std:
             EP_CUDA(cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
             s.opened.push_back(q);
             base = static_cast<char*>(q);
-        } else {
-            for (int i = 0; i < PEER_BUFFERS; i++)
-                if (off[i] != s.arena_off[i]) {
-                    err = "peer export blobs are not in rank order";
-                    return MOE_B200_ERR_INVALID;
-                }
         }
-        s.table.xgrp[p] = reinterpret_cast<uint16_t*>(base + off[0]);
-        s.table.yrecv[p] = reinterpret_cast<float*>(base + off[1]);
-        s.table.ctrl[p] = reinterpret_cast<int*>(base + off[2]);
-        s.table.ret[p] = reinterpret_cast<int2*>(base + off[3]);
+        s.table.xgrp[p] = reinterpret_cast<uint16_t*>(base + mine.off[0]);
+        s.table.yrecv[p] = reinterpret_cast<float*>(base + mine.off[1]);
+        s.table.ctrl[p] = reinterpret_cast<int*>(base + mine.off[2]);
+        s.table.ret[p] = reinterpret_cast<int2*>(base + mine.off[3]);
     }
     s.peer_enabled = true;
     return 0;

@@ -1,10 +1,12 @@
 // Grouped expert GEMMs on warp-level mma.sync -- the CROSS-CHECK implementation.
 //
 // Same inputs, outputs, weight layout and rounding points as the tcgen05
-// kernels in gemm_tc5.cuh, written as plainly as possible (single-buffered,
-// no TMA, no tensor memory) so that the two can be compared on the device at
-// sizes where the CPU oracle is too slow.  Selected with
-// moe_b200_config.gemm_impl = MOE_B200_GEMM_MMA_SYNC.
+// kernels (gemm_tc5_pair.cuh, gemm_tc5_swap.cuh), written as plainly as possible
+// (single-buffered, no TMA, no tensor memory) so that the two can be compared on
+// the device at sizes where the CPU oracle is too slow.  Compiled only into the
+// test-aids build of the library (-DMOE_B200_TEST_AIDS), where
+// moe_b200_config.gemm_impl = MOE_B200_GEMM_MMA_SYNC selects it; the shipped
+// library has the tcgen05 kernels only.
 //
 // MODE 0: gate/up projection + bias + clamped SwiGLU -> h bf16 [rows, I]
 //         (moe_mlp1_swiglu, src/hip/moe.hip:9-258; SwiGLU src/run.cpp:673-689)
@@ -27,15 +29,6 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// Clamped SwiGLU (src/run.cpp:673-689, src/hip/moe.hip:186-191).
-__device__ __forceinline__ float swiglu(float gate, float up, float alpha, float limit) {
-    const float g = fminf(gate, limit);
-    const float u = fminf(fmaxf(up, -limit), limit);
-    // fast reciprocal: the IEEE division costs ~90 cycles per value in the epilogue
-    const float sig = __fdividef(1.0f, 1.0f + __expf(-alpha * g));
-    return g * sig * (u + 1.0f);
-}
-
 // Locates the expert of n-tile `nt` in the prefix table tile_start[E+1].
 __device__ __forceinline__ int find_expert(const int* __restrict__ tile_start, int E, int nt) {
     int lo = 0, hi = E;  // invariant: tile_start[lo] <= nt < tile_start[hi]
@@ -56,8 +49,7 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
                        const uint16_t* __restrict__ xin, int K, const int* __restrict__ g_off,
                        const int* __restrict__ g_cnt, const int* __restrict__ g_tile_start, int E,
                        void* __restrict__ outp, int out_ld, int out_rows_valid,
-                       const int* __restrict__ row_dst, float* const* __restrict__ row_ptr,
-                       float alpha, float limit) {
+                       const int* __restrict__ row_dst, float alpha, float limit) {
     __shared__ __align__(16) uint16_t As[TILE_M * V0_LD];
     __shared__ __align__(16) uint16_t Bs[V0_BN * V0_LD];
 
@@ -177,9 +169,7 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
                     for (int c = 0; c < 2; c++) {
                         const int col = nh * 32 + nb * 8 + 2 * t + c;
                         if (col < valid_n) {
-                            float* yrow = row_ptr ? row_ptr[row0 + col]
-                                                  : y + (size_t)(row_dst ? row_dst[row0 + col]
-                                                                         : (row0 + col)) * out_ld;
+                            float* yrow = y + (size_t)(row_dst ? row_dst[row0 + col] : (row0 + col)) * out_ld;
                             yrow[m] = acc[a][nb][2 * half + c] + bm;
                         }
                     }

@@ -5,10 +5,15 @@
 //   MODE 1: y[rows, H]  = h[rows, I] . W2_e^T + b2_e              (fp32 out)
 //           moe_mlp2_store / moe_mlp2_scatter, src/hip/moe.hip:261-800
 //
-// Same inputs, outputs, weight layout and rounding points as gemm_tc5.cuh, whose
-// large-batch kernel is bound by the activation bytes every SM pulls through L2
-// (32 KB per 64 columns of K, ~47 B/cycle/SM).  Here a cluster of two CTAs works
-// on one item (expert, PAIR of 128-row weight tiles, tile of 256 token rows) with
+// One persistent cluster of two CTAs per SM pair walks a device-built list of
+// work items; no value is read back by the host (the reference sizes its grids
+// from a per-layer device->host copy, src/forward.cpp:340-345,381).
+//
+// Orientation: D[weight rows, token rows] = W_tile . X_tile^T: the decoded weight
+// tile is the UMMA A operand (TMEM lanes), the token rows the B operand, so a
+// ragged expert only narrows N.  A single CTA doing this is bound by the
+// activation bytes it pulls through L2 (32 KB per 64 columns of K, ~47 B/cycle/SM).
+// Here a cluster of two CTAs works on one item (expert, PAIR of 128-row weight tiles, tile of 256 token rows) with
 // one 256 x 256 x 16 MMA per instruction: each CTA decodes its own weight tile
 // (A operand, its 128 TMEM lanes) and loads only HALF of the token tile (B
 // operand: the tensor core reads rows 0..N/2-1 from the leader's shared memory and
@@ -28,9 +33,11 @@
 // Both CTAs allocate and free tensor memory (cta_group::2) and meet at a cluster
 // barrier before they exit, so no remote arrive can reach a CTA that has gone.
 //
-// Every mbarrier wait is bounded in time as in gemm_tc5.cuh.
+// Every mbarrier wait is bounded in time; a wait that runs out records a code in
+// the handle's status word, raises a CTA-wide abort flag and all roles fall
+// through to the common exit where tensor memory is released.
 #pragma once
-#include "gemm_mma.cuh"  // swiglu()
+#include "peer_io.cuh"
 #include "tc5_ptx.cuh"
 
 namespace moe {
@@ -155,7 +162,7 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
                         const int* __restrict__ g_off, const int* __restrict__ g_cnt,
                         const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
                         int out_ld, int out_rows_valid, const int* __restrict__ row_dst,
-                        float* const* __restrict__ row_ptr, float alpha, float limit,
+                        const __grid_constant__ peer::GemmPeerIO pio, float alpha, float limit,
                         int* __restrict__ status) {
     extern __shared__ unsigned char smem_dyn[];
     // slots need 1024-byte alignment for the 128-byte swizzle; the offsets are the
@@ -269,6 +276,17 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
             int i = 0, sb = 0, nb = 0, eb = 0;
             uint32_t phe = 0;
             bool ok = true;
+            if (MODE == 0 && pio.wait_flags) {
+                // expert-parallel peer mode: the rows of this GEMM are stored by the other
+                // GPUs; wait (bounded) until every rank has delivered, then order those
+                // generic-proxy writes before this thread's TMA loads
+                for (int p = 0; ok && p < pio.G; p++)
+                    ok = peer::wait_flag(pio.wait_flags + p, pio.seq, status);
+                __threadfence_system();
+                fence_proxy_async_global();
+                if (!ok)
+                    *abort_flag = 1;
+            }
             for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
                 const TileInfo ti = decode_tile(tile, m_pairs, tt, E);
                 const int half_row0 = ti.row0 + (int)rank * (ti.n_mma >> 1);
@@ -321,7 +339,7 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
             // ------------------------- leader: MMA issuer --------------------------
             // The whole warp runs the loop with no lane-divergent code but the elected
             // issue; the barrier of the NEXT step is tested before the MMAs of this
-            // step are issued (see gemm_tc5.cuh).
+            // step are issued, so that its latency overlaps the issue.
             int it = 0;
             bool ready = false;  // full[nb] already seen complete for phase ph
             for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs, ++it) {
@@ -522,8 +540,13 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
                                     // result row: on another GPU (peer mode), at a remapped row
                                     // (received order), or in place
                                     const int rr = ti.row0 + col;
-                                    float* yrow = row_ptr ? row_ptr[rr]
-                                                          : y + (size_t)(row_dst ? row_dst[rr] : rr) * out_ld;
+                                    float* yrow;
+                                    if (pio.ret) {
+                                        const int2 a = pio.ret[rr];
+                                        yrow = pio.yrecv[a.x] + (size_t)a.y * out_ld;
+                                    } else {
+                                        yrow = y + (size_t)(row_dst ? row_dst[rr] : rr) * out_ld;
+                                    }
                                     *reinterpret_cast<float4*>(yrow + m4) = val;
                                 }
                             }
@@ -543,6 +566,8 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
             if (warp == EPI_WARP0 && lane == 0)
                 TRACE(it * k_stages, 11);
         }
+        if (MODE == 1 && pio.ticket)
+            __threadfence_system();  // this thread's peer stores, before the CTA is counted below
     }
 
     // common exit: every role comes here, finished or aborted.  The cluster barrier
@@ -554,6 +579,15 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
     if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc2(tmem_base, TMEM_COLS);
+    }
+    if (MODE == 1 && pio.ticket && threadIdx.x == 0) {
+        // the last CTA to get here raises "results delivered" at every rank
+        if (atomicAdd(pio.ticket, 1) == (int)gridDim.x - 1) {
+            *pio.ticket = 0;
+            __threadfence_system();
+            for (int p = 0; p < pio.G; p++)
+                *reinterpret_cast<volatile int*>(pio.done_flags[p]) = pio.seq;
+        }
     }
 }
 

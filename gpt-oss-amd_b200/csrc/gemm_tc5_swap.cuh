@@ -5,7 +5,7 @@
 //   MODE 1: y[rows, H]  = h[rows, I] . W2_e^T + b2_e              (fp32 out)
 //           moe_mlp2_store / moe_mlp2_scatter, src/hip/moe.hip:261-800
 //
-// Same inputs, outputs, weight layout and rounding points as gemm_tc5.cuh, with
+// Same inputs, outputs, weight layout and rounding points as gemm_tc5_pair.cuh, with
 // the operand roles the other way round:
 //   D[128 token rows, 256 weight rows] = X_tile . W_tile^T
 // The token rows are the UMMA A operand (M = 128 TMEM lanes, fetched by TMA, a
@@ -16,7 +16,7 @@
 // tcgen05.mma covers 256 weight rows instead of 128, i.e. twice the weight bytes
 // per step of that chain.  The price is twice the decode work per FLOP (a decoded
 // weight tile is used by 128 token rows, not 256), which is why large batches
-// use gemm_tc5.cuh.
+// use gemm_tc5_pair.cuh.
 //
 // One persistent CTA per SM walks work items (expert, tile of 256 weight rows,
 // tile of 128 token rows).  Rings in shared memory:
@@ -41,7 +41,7 @@
 // in the handle's status word, raises a CTA-wide abort flag and all roles fall
 // through to the common exit where tensor memory is released.
 #pragma once
-#include "gemm_mma.cuh"  // swiglu()
+#include "peer_io.cuh"
 #include "tc5_ptx.cuh"
 
 namespace moe {
@@ -128,7 +128,7 @@ expert_gemm_swap_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
                        const int* __restrict__ g_off, const int* __restrict__ g_cnt,
                        const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
                        int out_ld, int out_rows_valid, const int* __restrict__ row_dst,
-                       float* const* __restrict__ row_ptr, float alpha, float limit,
+                       const __grid_constant__ peer::GemmPeerIO pio, float alpha, float limit,
                        int* __restrict__ status) {
     extern __shared__ unsigned char smem_dyn[];
     // slots need 1024-byte alignment for the 128-byte swizzle
@@ -227,6 +227,17 @@ expert_gemm_swap_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
             int i = 0, sx = 0, nb = 0, eb = 0;
             uint32_t phe = 0;
             bool ok = true;
+            if (MODE == 0 && pio.wait_flags) {
+                // expert-parallel peer mode: the rows of this GEMM are stored by the other
+                // GPUs; wait (bounded) until every rank has delivered, then order those
+                // generic-proxy writes before this thread's TMA loads
+                for (int p = 0; ok && p < pio.G; p++)
+                    ok = peer::wait_flag(pio.wait_flags + p, pio.seq, status);
+                __threadfence_system();
+                fence_proxy_async_global();
+                if (!ok)
+                    *abort_flag = 1;
+            }
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileInfo ti = decode_tile(tile, m_tiles, w_tiles, tt, E);
                 for (int ks = 0; ks < k_stages; ks++, i++) {
@@ -456,8 +467,12 @@ expert_gemm_swap_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
                 float* yrow = nullptr;
                 if (row_ok) {
                     const int rr = ti.row0 + row;
-                    yrow = row_ptr ? row_ptr[rr]
-                                   : static_cast<float*>(outp) + (size_t)(row_dst ? row_dst[rr] : rr) * out_ld;
+                    if (pio.ret) {
+                        const int2 a = pio.ret[rr];
+                        yrow = pio.yrecv[a.x] + (size_t)a.y * out_ld;
+                    } else {
+                        yrow = static_cast<float*>(outp) + (size_t)(row_dst ? row_dst[rr] : rr) * out_ld;
+                    }
                     yrow += n0;
                 }
                 for (int c0 = 0; c0 < n_cols; c0 += 32) {
@@ -482,6 +497,8 @@ expert_gemm_swap_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
             if (lane == 0)
                 mbar_arrive(bar_tmem_empty(set));
         }
+        if (MODE == 1 && pio.ticket)
+            __threadfence_system();  // this thread's peer stores, before the CTA is counted below
     }
 
     // common exit: every role comes here, finished or aborted
@@ -490,6 +507,15 @@ expert_gemm_swap_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
     if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (MODE == 1 && pio.ticket && threadIdx.x == 0) {
+        // the last CTA to get here raises "results delivered" at every rank
+        if (atomicAdd(pio.ticket, 1) == (int)gridDim.x - 1) {
+            *pio.ticket = 0;
+            __threadfence_system();
+            for (int p = 0; p < pio.G; p++)
+                *reinterpret_cast<volatile int*>(pio.done_flags[p]) = pio.seq;
+        }
     }
 }
 

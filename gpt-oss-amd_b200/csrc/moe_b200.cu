@@ -12,8 +12,9 @@
 
 #include "common.cuh"
 #include "ep.cuh"
+#ifdef MOE_B200_TEST_AIDS
 #include "gemm_mma.cuh"
-#include "gemm_tc5.cuh"
+#endif
 #include "gemm_tc5_pair.cuh"
 #include "gemm_tc5_swap.cuh"
 #include "mxfp4.cuh"
@@ -86,6 +87,7 @@ struct moe_b200_handle_s {
     // per-stage timing: event pairs for `prof_armed` forwards
     std::vector<cudaEvent_t> prof_ev;
     int prof_armed = 0, prof_next = 0, prof_call = -1;
+    bool prof_external = false;  // the host-buffer entry point picked prof_call for the forward it wraps
 
     std::string err;
     int last_launches = 0;
@@ -183,8 +185,33 @@ constexpr int ROUTE_SMALL_MAX_TOKENS = 1024;
 constexpr int TC5_BN = 256;                   // token rows per tile of the large-batch GEMM
 constexpr int SWAP_MAX_ROWS_PER_EXPERT = 96;  // at most this many rows per expert: small-batch GEMM
 
+// Largest hidden size the warp-per-token router stages in shared memory.
+constexpr size_t ROUTE_SMALL_SMEM_LIMIT = 200 * 1024;
+
 int route_block_tokens(int T, int H) {
-    return (T <= ROUTE_SMALL_MAX_TOKENS && route_small_smem_bytes(H) <= 200 * 1024) ? RBS : RB;
+    return (T <= ROUTE_SMALL_MAX_TOKENS && route_small_smem_bytes(H) <= ROUTE_SMALL_SMEM_LIMIT) ? RBS : RB;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to (device, kernel), not to
+// a handle: every user of route_small_kernel<NT> -- any handle's forward and the
+// handle-free moe_b200_route_noalloc -- raises it through this one function, once
+// per device and instantiation, to the largest size any of them can ask for, so
+// that no later caller can lower the limit under an earlier one.
+constexpr int MAX_DEVICES = 64;
+int g_route_small_attr[MAX_DEVICES];  // bit per NT instantiation
+
+template <int NT>
+cudaError_t ensure_route_small_attr(int dev) {
+    const int bit = NT == 1 ? 1 : NT == 2 ? 2 : NT == 4 ? 4 : 8;
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return cudaErrorInvalidDevice;
+    if (g_route_small_attr[dev] & bit)
+        return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(route_small_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)ROUTE_SMALL_SMEM_LIMIT);
+    if (e == cudaSuccess)
+        g_route_small_attr[dev] |= bit;
+    return e;
 }
 
 template <int NT>
@@ -192,14 +219,12 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
                              const LayerWeights& lw, float* score_out, int nblk, cudaStream_t st) {
     if (route_block_tokens(T, h->cfg.hidden_dim) == RBS) {
         const size_t smem = route_small_smem_bytes(h->cfg.hidden_dim);
-        if (!(h->smem_attr_done & 8)) {
-            CU_TRY(h, cudaFuncSetAttribute(route_small_kernel<NT>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            h->smem_attr_done |= 8;
-        }
+        CU_TRY(h, ensure_route_small_attr<NT>(h->cfg.device));
         route_small_kernel<NT><<<nblk, RBS * 32, smem, st>>>(
             t, t_dtype == MOE_B200_DTYPE_F32, T, h->cfg.hidden_dim, lw.w_router, lw.b_router,
             h->cfg.n_experts, h->cfg.experts_per_token, score_out, h->topk_i, h->topk_w, h->blk_hist);
+        // a launch that failed must not be followed by kernels that consume its output
+        CU_TRY(h, cudaGetLastError());
         return MOE_B200_OK;
     }
     if constexpr (NT <= 4) {
@@ -208,10 +233,12 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
                                                         h->cfg.hidden_dim, lw.w_router, lw.b_router,
                                                         h->cfg.n_experts, h->cfg.experts_per_token,
                                                         score_out, h->topk_i, h->topk_w, h->blk_hist);
+        CU_TRY(h, cudaGetLastError());
         return MOE_B200_OK;
     }
     const size_t smem = route_smem_bytes<NT>();
     if (!(h->smem_attr_done & 16) && smem > 48 * 1024) {
+        // the size depends on NT only: every handle sets the same value
         CU_TRY(h, cudaFuncSetAttribute(route_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     }
@@ -220,35 +247,7 @@ moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int 
                                                    h->cfg.hidden_dim, lw.w_router, lw.b_router,
                                                    h->cfg.n_experts, h->cfg.experts_per_token,
                                                    score_out, h->topk_i, h->topk_w, h->blk_hist);
-    return MOE_B200_OK;
-}
-
-// Large batches: weights on the TMEM lanes, 256 token rows per tile (gemm_tc5.cuh).
-moe_b200_status launch_tc5(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
-                           const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
-                           const int* row_dst, float* const* row_ptr, cudaStream_t st) {
-    const moe_b200_config& c = h->cfg;
-    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
-    constexpr int BN = TC5_BN;
-    constexpr int smem = tc5::smem_bytes<BN>();
-    if (!(h->smem_attr_done & 1)) {  // per handle: the attribute is per device
-        CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<0, BN>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        CU_TRY(h, cudaFuncSetAttribute(tc5::expert_gemm_tc5_kernel<1, BN>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        h->smem_attr_done |= 1;
-    }
-    prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
-    tc5::expert_gemm_tc5_kernel<0, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
-        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-        EL, h->hbuf, I, I, nullptr, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
-    prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
-    prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
-    tc5::expert_gemm_tc5_kernel<1, BN><<<h->n_sms, tc5::n_threads<BN>(), smem, st>>>(
-        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
-        EL, yout, H, H, row_dst, row_ptr, c.swiglu_alpha, c.swiglu_limit, h->status);
-    prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
-    h->last_launches += 2;
+    CU_TRY(h, cudaGetLastError());
     return MOE_B200_OK;
 }
 
@@ -259,7 +258,7 @@ moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
                                    int ks, int m_tiles, const float* bias, int bias_stride,
                                    const int* g_off, const int* g_cnt, const int* g_tile_start, int EL,
                                    void* out, int out_ld, int out_valid, const int* row_dst,
-                                   float* const* row_ptr) {
+                                   const peer::GemmPeerIO& pio) {
     namespace pr = tc5::pair;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -275,13 +274,13 @@ moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
     cfg.numAttrs = 1;
     CU_TRY(h, cudaLaunchKernelEx(&cfg, pr::expert_gemm_pair_kernel<MODE>, maps, chunks, stride, ks, m_tiles,
                                  bias, bias_stride, g_off, g_cnt, g_tile_start, EL, out, out_ld, out_valid,
-                                 row_dst, row_ptr, h->cfg.swiglu_alpha, h->cfg.swiglu_limit, h->status));
+                                 row_dst, pio, h->cfg.swiglu_alpha, h->cfg.swiglu_limit, h->status));
     return MOE_B200_OK;
 }
 
 moe_b200_status launch_pair(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
                             const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
-                            const int* row_dst, float* const* row_ptr, cudaStream_t st) {
+                            const int* row_dst, const peer::GemmPeerIO& pio, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
     namespace pr = tc5::pair;
@@ -312,13 +311,13 @@ moe_b200_status launch_pair(moe_b200_handle h, const LayerWeights& lw, const tc5
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
     moe_b200_status s1 = launch_pair_kernel<0>(h, h->pair_grid, st, maps_x, lw.w1, h->stride1, h->ks1,
                                                h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-                                               EL, h->hbuf, I, I, nullptr, nullptr);
+                                               EL, h->hbuf, I, I, nullptr, pio);
     if (s1)
         return s1;
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
     s1 = launch_pair_kernel<1>(h, h->pair_grid, st, h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2,
-                               lw.bias2, H, g_off, g_cnt, g_tile_start, EL, yout, H, H, row_dst, row_ptr);
+                               lw.bias2, H, g_off, g_cnt, g_tile_start, EL, yout, H, H, row_dst, pio);
     if (s1)
         return s1;
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
@@ -329,7 +328,7 @@ moe_b200_status launch_pair(moe_b200_handle h, const LayerWeights& lw, const tc5
 // Small batches: token rows on the TMEM lanes, 256 weight rows per tile (gemm_tc5_swap.cuh).
 moe_b200_status launch_swap(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
                             const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
-                            const int* row_dst, float* const* row_ptr, cudaStream_t st) {
+                            const int* row_dst, const peer::GemmPeerIO& pio, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
     namespace sw = tc5::swp;
@@ -343,12 +342,12 @@ moe_b200_status launch_swap(moe_b200_handle h, const LayerWeights& lw, const tc5
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
     sw::expert_gemm_swap_kernel<0><<<h->n_sms, sw::N_THREADS, sw::SMEM_BYTES, st>>>(
         maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-        EL, h->hbuf, I, I, nullptr, nullptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+        EL, h->hbuf, I, I, nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
     sw::expert_gemm_swap_kernel<1><<<h->n_sms, sw::N_THREADS, sw::SMEM_BYTES, st>>>(
         h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
-        EL, yout, H, H, row_dst, row_ptr, c.swiglu_alpha, c.swiglu_limit, h->status);
+        EL, yout, H, H, row_dst, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
     h->last_launches += 2;
     return MOE_B200_OK;
@@ -361,35 +360,40 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
                              const tc5::TensorMaps& maps_x, int rows_upper, int bn,
                              const int* g_off,
                              const int* g_cnt, const int* g_tile_start, float* yout,
-                             const int* row_dst, float* const* row_ptr, cudaStream_t st) {
+                             const int* row_dst, const peer::GemmPeerIO& pio, cudaStream_t st) {
     const moe_b200_config& c = h->cfg;
     const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+#ifdef MOE_B200_TEST_AIDS
     if (c.gemm_impl == MOE_B200_GEMM_MMA_SYNC) {
+        if (pio.ret)
+            return fail(h, MOE_B200_ERR_UNSUPPORTED,
+                        "the cross-check GEMM does not take part in the peer-memory exchange");
         const int n_tiles_upper = rows_upper / V0_BN + EL;
         dim3 g1(n_tiles_upper, h->m_tiles1), g2(n_tiles_upper, h->m_tiles2);
         prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
         expert_gemm_mma_kernel<0><<<g1, 256, 0, st>>>(lw.w1, h->stride1, h->ks1, lw.bias1, 2 * I, xin,
                                                       H, g_off, g_cnt, g_tile_start, EL, h->hbuf, I,
-                                                      I, nullptr, nullptr, c.swiglu_alpha,
-                                                      c.swiglu_limit);
+                                                      I, nullptr, c.swiglu_alpha, c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
         prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
         expert_gemm_mma_kernel<1><<<g2, 256, 0, st>>>(lw.w2, h->stride2, h->ks2, lw.bias2, H, h->hbuf,
                                                       I, g_off, g_cnt, g_tile_start, EL, yout, H, H,
-                                                      row_dst, row_ptr, c.swiglu_alpha,
-                                                      c.swiglu_limit);
+                                                      row_dst, c.swiglu_alpha, c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
-    } else if (bn == tc5::swp::BM) {
-        return launch_swap(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
-    } else if (bn == TC5_BN && c.gemm_impl == MOE_B200_GEMM_TCGEN05_1CTA) {
-        return launch_tc5(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
-    } else if (bn == TC5_BN) {
-        return launch_pair(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, row_ptr, st);
-    } else {
-        return fail(h, MOE_B200_ERR_INVALID, "tile tables were built for another tile height");
+        h->last_launches += 2;
+        return MOE_B200_OK;
     }
-    h->last_launches += 2;
-    return MOE_B200_OK;
+#endif
+    (void)xin;
+    (void)rows_upper;
+    (void)H;
+    (void)I;
+    (void)EL;
+    if (bn == tc5::swp::BM)
+        return launch_swap(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
+    if (bn == TC5_BN)
+        return launch_pair(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
+    return fail(h, MOE_B200_ERR_INVALID, "tile tables were built for another tile height");
 }
 
 // Blocks per routing block of the permute kernels: about sixteen blocks per SM (measured at
@@ -405,8 +409,10 @@ int permute_split(moe_b200_handle h, int nblk, int n_assign) {
 // rows on the TMEM lanes, 128 per tile; otherwise weights on the lanes and 256
 // token rows per tile.  Any choice is correct for any distribution of rows.
 int pick_bn(moe_b200_handle h, int rows) {
+#ifdef MOE_B200_TEST_AIDS
     if (h->cfg.gemm_impl == MOE_B200_GEMM_MMA_SYNC)
         return V0_BN;
+#endif
     const int per_expert = rows / (h->n_local > 0 ? h->n_local : 1);
     return per_expert <= SWAP_MAX_ROWS_PER_EXPERT ? tc5::swp::BM : TC5_BN;
 }
@@ -417,7 +423,13 @@ int pick_bn(moe_b200_handle h, int rows) {
 
 extern "C" {
 
-const char* moe_b200_version(void) { return "moe_b200 0.1 sm_100a"; }
+const char* moe_b200_version(void) {
+#ifdef MOE_B200_TEST_AIDS
+    return "moe_b200 0.2 sm_100a test-aids";
+#else
+    return "moe_b200 0.2 sm_100a";
+#endif
+}
 
 void moe_b200_shard_range(int n_experts, int ep_size, int ep_rank, int* first_expert, int* n_local) {
     // src/model.cpp:104-114: contiguous blocks, remainder to the low ranks
@@ -452,9 +464,15 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         return fail(nullptr, MOE_B200_ERR_INVALID, "n_layers and max_tokens must be positive");
     if (c.ep_size <= 0 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.ep_size > c.n_experts)
         return fail(nullptr, MOE_B200_ERR_INVALID, "bad ep_rank / ep_size");
-    if (c.gemm_impl != MOE_B200_GEMM_TCGEN05 && c.gemm_impl != MOE_B200_GEMM_MMA_SYNC &&
-        c.gemm_impl != MOE_B200_GEMM_TCGEN05_1CTA)
+#ifdef MOE_B200_TEST_AIDS
+    if (c.gemm_impl != MOE_B200_GEMM_TCGEN05 && c.gemm_impl != MOE_B200_GEMM_MMA_SYNC)
         return fail(nullptr, MOE_B200_ERR_INVALID, "unknown gemm_impl");
+#else
+    if (c.gemm_impl != MOE_B200_GEMM_TCGEN05)
+        return fail(nullptr, MOE_B200_ERR_INVALID,
+                    "gemm_impl must be MOE_B200_GEMM_TCGEN05 (the cross-check kernel exists only in "
+                    "the test-aids build)");
+#endif
 
     int n_dev = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
@@ -519,7 +537,7 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         (st = dev_alloc(h, &h->tile_start, E + 1)) || (st = dev_alloc(h, &h->slot_of, TK)) ||
         (st = dev_alloc(h, &h->row_token, TK)) || (st = dev_alloc(h, &h->xs, TK * H)) ||
         (st = dev_alloc(h, &h->hbuf, (size_t)h->rows_cap * I)) ||
-        (st = dev_alloc(h, &h->ybuf, (size_t)h->rows_cap * H)) || (st = dev_alloc(h, &h->status, 1)) ||
+        (st = dev_alloc(h, &h->status, 2)) ||
         (st = dev_alloc(h, (float**)&h->t_dev, (size_t)c.max_tokens * H)) ||
         (st = dev_alloc(h, &h->out_dev, (size_t)c.max_tokens * H)) ||
         (st = dev_alloc(h, &h->stage_blocks, (size_t)2 * I * (H / 32) * 16 > (size_t)H * (I / 32) * 16
@@ -529,7 +547,11 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
                                                  ? (size_t)2 * I * (H / 32)
                                                  : (size_t)H * (I / 32))))
         return bail(st);
-    if (cudaMemset(h->status, 0, sizeof(int)) != cudaSuccess ||
+    // fp32 rows of the down GEMM before the combine: only the single-GPU path keeps
+    // them here (expert-parallel results go to the token owner's receive buffer)
+    if (c.ep_size == 1 && (st = dev_alloc(h, &h->ybuf, (size_t)h->rows_cap * H)))
+        return bail(st);
+    if (cudaMemset(h->status, 0, 2 * sizeof(int)) != cudaSuccess ||
         cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
         return bail(fail(h, MOE_B200_ERR_CUDA, "stream / memset failed"));
     if (c.ep_size > 1) {
@@ -538,7 +560,7 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         if (st)
             return bail(st);
     }
-    if (c.gemm_impl != MOE_B200_GEMM_MMA_SYNC) {
+    {
         void* x_base = (c.ep_size > 1) ? (void*)h->ep.xgrp : (void*)h->xs;
         const int x_rows = (c.ep_size > 1) ? h->rows_cap : (int)TK;
         if ((st = make_maps(h, &h->maps_x, x_base, H, x_rows)) ||
@@ -611,44 +633,49 @@ moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int fir
     const size_t nb2 = (size_t)H * G2 * 16, ns2 = (size_t)H * G2;
     const bool dev1 = is_device_pointer(blocks1) && is_device_pointer(scales1);
     const bool dev2 = is_device_pointer(blocks2) && is_device_pointer(scales2);
+    // Everything is queued on one stream (copy -> re-tile -> next copy into the same
+    // staging buffer are ordered by it) and the host waits once, at the end.
+    cudaStream_t s = h->own_stream;
+    int* bad_scale = h->status + 1;  // its own word: an older wait code cannot mask it
+    CU_TRY(h, cudaMemsetAsync(bad_scale, 0, sizeof(int), s));
     for (int i = 0; i < n; i++) {
         const int le = first_expert + i - h->first_expert;
         const uint8_t *b1 = blocks1 + i * nb1, *s1 = scales1 + i * ns1;
         const uint8_t *b2 = blocks2 + i * nb2, *s2 = scales2 + i * ns2;
         if (!dev1) {
-            CU_TRY(h, cudaMemcpy(h->stage_blocks, b1, nb1, cudaMemcpyHostToDevice));
-            CU_TRY(h, cudaMemcpy(h->stage_scales, s1, ns1, cudaMemcpyHostToDevice));
+            CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b1, nb1, cudaMemcpyHostToDevice, s));
+            CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s1, ns1, cudaMemcpyHostToDevice, s));
             b1 = h->stage_blocks;
             s1 = h->stage_scales;
         }
-        mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M>>>(b1, s1, 2 * I, G1,
-                                                                   lw.w1 + le * h->stride1, h->status);
-        CU_TRY(h, cudaDeviceSynchronize());
+        mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(b1, s1, 2 * I, G1,
+                                                                         lw.w1 + le * h->stride1, bad_scale);
         if (!dev2) {
-            CU_TRY(h, cudaMemcpy(h->stage_blocks, b2, nb2, cudaMemcpyHostToDevice));
-            CU_TRY(h, cudaMemcpy(h->stage_scales, s2, ns2, cudaMemcpyHostToDevice));
+            CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b2, nb2, cudaMemcpyHostToDevice, s));
+            CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s2, ns2, cudaMemcpyHostToDevice, s));
             b2 = h->stage_blocks;
             s2 = h->stage_scales;
         }
-        mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M>>>(b2, s2, H, G2,
-                                                                   lw.w2 + le * h->stride2, h->status);
-        CU_TRY(h, cudaDeviceSynchronize());
-        CU_TRY(h, cudaMemcpy(lw.bias1 + (size_t)le * 2 * I, bias1 + (size_t)i * 2 * I,
-                             (size_t)2 * I * 4, cudaMemcpyDefault));
-        CU_TRY(h, cudaMemcpy(lw.bias2 + (size_t)le * H, bias2 + (size_t)i * H, (size_t)H * 4,
-                             cudaMemcpyDefault));
-        lw.expert_set[le] = 1;
+        mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(b2, s2, H, G2,
+                                                                         lw.w2 + le * h->stride2, bad_scale);
+        CU_TRY(h, cudaMemcpyAsync(lw.bias1 + (size_t)le * 2 * I, bias1 + (size_t)i * 2 * I,
+                                  (size_t)2 * I * 4, cudaMemcpyDefault, s));
+        CU_TRY(h, cudaMemcpyAsync(lw.bias2 + (size_t)le * H, bias2 + (size_t)i * H, (size_t)H * 4,
+                                  cudaMemcpyDefault, s));
     }
+    CU_TRY(h, cudaGetLastError());
     int sw = 0;
-    CU_TRY(h, cudaMemcpy(&sw, h->status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (sw == DS_BAD_SCALE) {
-        CU_TRY(h, cudaMemset(h->status, 0, sizeof(int)));
+    CU_TRY(h, cudaMemcpyAsync(&sw, bad_scale, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    if (sw != 0) {
         for (int i = 0; i < n; i++)
             lw.expert_set[first_expert + i - h->first_expert] = 0;
         return fail(h, MOE_B200_ERR_UNSUPPORTED,
                     "an e8m0 scale byte above 128 (block scale above 2) was found; the in-kernel "
                     "decode covers scale bytes 0..128");
     }
+    for (int i = 0; i < n; i++)
+        lw.expert_set[first_expert + i - h->first_expert] = 1;
     return MOE_B200_OK;
 }
 
@@ -682,7 +709,8 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     const int nblk = ceil_div(T, rb);
     const int bn_local = pick_bn(h, T * K);  // ep_size == 1: the GEMMs run on this rank's own rows
     h->last_launches = 0;
-    h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
+    if (!h->prof_external)
+        h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
 
     if (T > 0) {
         prof_mark(h, MOE_B200_STAGE_ROUTE, true, s);
@@ -701,83 +729,96 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
         h->last_launches++;
     }
     // plan + permute also run for T == 0 on an expert-parallel rank (nblk == 0
-    // gives all-zero counts), so that the collective below always has its inputs
-    prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
-    plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off, h->tile_start,
-                                  h->blk_base);
-    prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
-    h->last_launches++;
-    if (T > 0 && !peer_mode) {
-        prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
-        permute_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb,
-                                            h->topk_i, h->blk_base, h->slot_of, h->row_token, h->xs,
-                                            h->status);
-        prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
-        h->last_launches++;
-    }
-
+    // gives all-zero counts), so that the exchange below always has its inputs
+    const peer::GemmPeerIO no_peer{};
     const float* y_for_combine = h->ybuf;
+    const int* combine_wait = nullptr;
+    int seq = 0;
     if (peer_mode) {
-        // exchange fused into the permute kernel and the down GEMM's epilogue (ep_peer.cuh)
+        // exchange fused into the plan / permute kernels, the GEMMs and the combine (ep_peer.cuh)
         ep::State& es = h->ep;
         const int G = c.ep_size, rank = c.ep_rank;
-        const int seq = ++es.seq;
+        seq = ++es.seq;
         const int bn = pick_bn(h, (T > 0 ? T : c.max_tokens) * K);  // rows here are not known on the host
+        prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
+        peer::plan_publish_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off,
+                                                    h->tile_start, h->blk_base, G, rank, es.table, seq);
+        prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
         prof_mark(h, MOE_B200_STAGE_DISPATCH, true, s);
-        peer::publish_counts_kernel<<<1, 256, 0, s>>>(h->cnt, E, G, rank, es.table, seq);
-        peer::wait_counts_plan_kernel<<<1, 256, 0, s>>>(E, G, rank, bn, es.table, seq, es.g_cnt, es.g_off,
-                                                        es.g_tile_start, es.send_base, h->status);
-        if (T > 0)
-            peer::permute_to_peers_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(
-                t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, G, rank, rb, h->topk_i, h->blk_base,
-                h->off, es.send_base, es.table, h->slot_of, h->status);
-        peer::barrier_kernel<<<1, 32, 0, s>>>(1, E, G, rank, es.table, seq, h->status);
+        const int gx = nblk > 0 ? nblk : 1;
+        peer::permute_to_peers_kernel<<<dim3(gx, T > 0 ? permute_split(h, nblk, rb * K) : 1), 256, 0, s>>>(
+            t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, G, rank, rb, bn, h->rows_cap, h->topk_i,
+            h->blk_base, h->off, es.table, seq, h->slot_of, es.g_cnt, es.g_off, es.g_tile_start,
+            es.tickets, h->status);
         prof_mark(h, MOE_B200_STAGE_DISPATCH, false, s);
-        prof_mark(h, MOE_B200_STAGE_REGROUP, true, s);
-        peer::row_pointers_kernel<<<h->n_sms, 256, 0, s>>>(es.g_off, h->n_local, H, es.table, rank,
-                                                           es.row_ptr);
-        prof_mark(h, MOE_B200_STAGE_REGROUP, false, s);
-        h->last_launches += (T > 0 ? 5 : 4);
+        h->last_launches += 2;
+        peer::GemmPeerIO pio{};
+        pio.wait_flags = peer::flag_slot(es.table.ctrl[rank], E, G, peer::FLAG_ROWS, 0);
+        pio.ret = es.table.ret[rank];
+        for (int p = 0; p < G; p++) {
+            pio.yrecv[p] = es.table.yrecv[p];
+            pio.done_flags[p] = peer::flag_slot(es.table.ctrl[p], E, G, peer::FLAG_RESULTS, rank);
+        }
+        pio.ticket = es.tickets + 1;
+        pio.G = G;
+        pio.seq = seq;
         st = launch_gemms(h, lw, es.xgrp, h->maps_x, h->rows_cap, bn, es.g_off, es.g_cnt,
-                          es.g_tile_start, nullptr, nullptr, es.row_ptr, s);
+                          es.g_tile_start, nullptr, nullptr, pio, s);
         if (st)
             return st;
-        prof_mark(h, MOE_B200_STAGE_RETURN, true, s);
-        peer::barrier_kernel<<<1, 32, 0, s>>>(2, E, G, rank, es.table, seq, h->status);
-        prof_mark(h, MOE_B200_STAGE_RETURN, false, s);
-        h->last_launches++;
         y_for_combine = es.yrecv;
-    } else if (c.ep_size == 1) {
+        combine_wait = peer::flag_slot(es.table.ctrl[rank], E, G, peer::FLAG_RESULTS, 0);
+    } else {
+        prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
+        plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off, h->tile_start,
+                                      h->blk_base);
+        prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
+        h->last_launches++;
         if (T > 0) {
-            st = launch_gemms(h, lw, h->xs, h->maps_x, T * K, bn_local, h->off, h->cnt, h->tile_start,
-                              h->ybuf, nullptr, nullptr, s);
+            prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
+            permute_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(
+                t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb, h->topk_i, h->blk_base, h->slot_of,
+                h->row_token, h->xs, h->status);
+            prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
+            h->last_launches++;
+        }
+        if (c.ep_size == 1) {
+            if (T > 0) {
+                st = launch_gemms(h, lw, h->xs, h->maps_x, T * K, bn_local, h->off, h->cnt, h->tile_start,
+                                  h->ybuf, nullptr, no_peer, s);
+                if (st)
+                    return st;
+            }
+        } else {
+            ep::GemmLauncher gl = [&](const uint16_t* xin, int rows_upper, int bn, const int* g_off,
+                                      const int* g_cnt, const int* g_tile_start, float* yout,
+                                      const int* row_dst) -> int {
+                return (int)launch_gemms(h, lw, xin, h->maps_x, rows_upper, bn, g_off, g_cnt,
+                                         g_tile_start, yout, row_dst, no_peer, s);
+            };
+            ep::PickBn pick = [&](int rows) { return pick_bn(h, rows); };
+            int launches = 0;
+            ep::StageMark mark = [&](int stage, bool begin) { prof_mark(h, stage, begin, s); };
+            st = (moe_b200_status)ep::exchange_and_compute(h->ep, c, h->n_local, h->first_expert, pick,
+                                                           T, h->cnt, h->xs, gl, mark, &y_for_combine, s,
+                                                           &launches, h->err);
+            h->last_launches += launches;
             if (st)
                 return st;
         }
-    } else {
-        ep::GemmLauncher gl = [&](const uint16_t* xin, int rows_upper, int bn, const int* g_off,
-                                  const int* g_cnt, const int* g_tile_start, float* yout,
-                                  const int* row_dst) -> int {
-            return (int)launch_gemms(h, lw, xin, h->maps_x, rows_upper, bn, g_off, g_cnt,
-                                     g_tile_start, yout, row_dst, nullptr, s);
-        };
-        ep::PickBn pick = [&](int rows) { return pick_bn(h, rows); };
-        int launches = 0;
-        ep::StageMark mark = [&](int stage, bool begin) { prof_mark(h, stage, begin, s); };
-        st = (moe_b200_status)ep::exchange_and_compute(h->ep, c, h->n_local, h->first_expert, pick,
-                                                       T, h->cnt, h->xs, gl, mark, &y_for_combine, s,
-                                                       &launches, h->err);
-        h->last_launches += launches;
-        if (st)
-            return st;
     }
 
-    if (T > 0) {
+    if (T > 0 || combine_wait) {
+        // peer mode launches it for T == 0 as well: the wait inside is what orders this
+        // rank's next call behind the peers' reads of this one
         prof_mark(h, MOE_B200_STAGE_COMBINE, true, s);
-        combine_kernel<<<T, 256, 0, s>>>(y_for_combine, T, H, K, h->topk_i, h->topk_w, h->slot_of,
-                                         out, accumulate);
+        combine_kernel<<<T > 0 ? T : 1, 256, 0, s>>>(y_for_combine, T, H, K, h->topk_i, h->topk_w,
+                                                     h->slot_of, out, accumulate, combine_wait,
+                                                     c.ep_size, seq, h->status);
         prof_mark(h, MOE_B200_STAGE_COMBINE, false, s);
         h->last_launches++;
+    }
+    if (T > 0) {
         if (topk_i_out)
             CU_TRY(h, cudaMemcpyAsync(topk_i_out, h->topk_i, (size_t)T * K * 4, cudaMemcpyDeviceToDevice, s));
         if (topk_w_out)
@@ -817,12 +858,22 @@ moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* 
         }
     }
     if (chunk >= n_tokens) {
+        // one pass; with profiling armed the two copies are timed as stages of the call
+        h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
+        h->prof_external = true;
+        struct Release {
+            moe_b200_handle h;
+            ~Release() { h->prof_external = false; }
+        } release{h};
+        prof_mark(h, MOE_B200_STAGE_H2D, true, s);
         if (n_tokens > 0)
             CU_TRY(h, cudaMemcpyAsync(h->t_dev, t_host, (size_t)n_tokens * H * esz, cudaMemcpyHostToDevice, s));
+        prof_mark(h, MOE_B200_STAGE_H2D, false, s);
         st = moe_b200_forward(h, layer, h->t_dev, t_dtype, n_tokens, h->out_dev, 0, nullptr, nullptr,
                               nullptr, reinterpret_cast<moe_b200_stream>(s));
         if (st)
             return st;
+        prof_mark(h, MOE_B200_STAGE_D2H, true, s);
         if (n_tokens > 0) {
             CU_TRY(h, cudaMemcpyAsync(out_host, h->out_dev, (size_t)n_tokens * H * 4, cudaMemcpyDeviceToHost, s));
             if (topk_i_host)
@@ -830,6 +881,7 @@ moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* 
             if (topk_w_host)
                 CU_TRY(h, cudaMemcpyAsync(topk_w_host, h->topk_w, (size_t)n_tokens * K * 4, cudaMemcpyDeviceToHost, s));
         }
+        prof_mark(h, MOE_B200_STAGE_D2H, false, s);
         CU_TRY(h, cudaStreamSynchronize(s));
         return MOE_B200_OK;
     }
@@ -887,7 +939,7 @@ moe_b200_status moe_b200_ep_peer_export(moe_b200_handle h, char* blob_out) {
     if (h->cfg.ep_size <= 1)
         return fail(h, MOE_B200_ERR_INVALID, "handle was created with ep_size == 1");
     CU_TRY(h, cudaSetDevice(h->cfg.device));
-    return (moe_b200_status)ep::peer_export(h->ep, blob_out, h->err);
+    return (moe_b200_status)ep::peer_export(h->ep, h->cfg, blob_out, h->err);
 }
 
 moe_b200_status moe_b200_ep_peer_enable(moe_b200_handle h, const char* all_blobs) {
@@ -905,12 +957,32 @@ moe_b200_status moe_b200_ep_init(moe_b200_handle h, const char id[128]) {
     if (h->cfg.ep_size <= 1)
         return fail(h, MOE_B200_ERR_INVALID, "handle was created with ep_size == 1");
     CU_TRY(h, cudaSetDevice(h->cfg.device));
+    moe_b200_status st = (moe_b200_status)ep::allocate_nccl(h->ep, h->cfg, h->allocs, h->device_bytes, h->err);
+    if (st)
+        return st;
     return (moe_b200_status)ep::init(h->ep, id, h->cfg.ep_size, h->cfg.ep_rank, h->err);
 }
 
 void moe_b200_ep_plan(int n_experts, int ep_size, int ep_rank, const int* cnt_all, int* send_cnt,
                       int* send_off, int* recv_cnt, int* recv_off) {
     ep::plan_exchange(n_experts, ep_size, ep_rank, cnt_all, send_cnt, send_off, recv_cnt, recv_off);
+}
+
+int moe_b200_ep_peer_sequence(moe_b200_handle h) { return h ? h->ep.seq : 0; }
+
+moe_b200_status moe_b200_ep_peer_resync(moe_b200_handle h, int sequence) {
+    if (!h)
+        return MOE_B200_ERR_INVALID;
+    if (!h->ep.peer_enabled)
+        return fail(h, MOE_B200_ERR_INVALID, "the peer-memory exchange is not enabled on this handle");
+    if (sequence < h->ep.seq)
+        return fail(h, MOE_B200_ERR_INVALID, "the sequence number can only move forward");
+    CU_TRY(h, cudaSetDevice(h->cfg.device));
+    CU_TRY(h, cudaDeviceSynchronize());
+    // finished-block counters of a call that was cut short start from zero again
+    CU_TRY(h, cudaMemset(h->ep.tickets, 0, 2 * sizeof(int)));
+    h->ep.seq = sequence;
+    return MOE_B200_OK;
 }
 
 size_t moe_b200_device_bytes(moe_b200_handle h) { return h ? h->device_bytes : 0; }
@@ -925,6 +997,8 @@ moe_b200_status moe_b200_device_status(moe_b200_handle h, int* status_word) {
     CU_TRY(h, cudaSetDevice(h->cfg.device));
     CU_TRY(h, cudaDeviceSynchronize());
     CU_TRY(h, cudaMemcpy(status_word, h->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status_word != 0)  // read and clear: the next report starts from a clean word
+        CU_TRY(h, cudaMemset(h->status, 0, sizeof(int)));
     if (*status_word != 0)
         return fail(h, MOE_B200_ERR_DEVICE,
                     "device status word = 0x" + [&] {
@@ -1029,7 +1103,7 @@ namespace {
 constexpr int NA_MAX_BLOCKS = MOE_B200_ROUTE_NOALLOC_MAX_TOKENS / RBS;  // routing blocks of RBS tokens
 constexpr int NA_HIST_INTS = NA_MAX_BLOCKS * MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS;
 constexpr int NA_SCRATCH_INTS = 2 * NA_HIST_INTS + MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS + 1;
-constexpr int NA_MAX_DEVICES = 64;
+constexpr int NA_MAX_DEVICES = MAX_DEVICES;
 
 // [0, NA_HIST_INTS)              per-block expert histograms (router kernel -> plan kernel)
 // [NA_HIST_INTS, 2*NA_HIST_INTS) per-block row bases (written by the plan kernel, unused here)
@@ -1040,20 +1114,16 @@ constexpr int NA_MAX_DEVICES = 64;
 static __device__ __align__(256) int g_route_noalloc_scratch[NA_SCRATCH_INTS];
 
 int* g_na_scratch_ptr[NA_MAX_DEVICES];  // per device, filled by the first call there
-int g_na_attr_done[NA_MAX_DEVICES];     // bit per router-kernel instantiation
 
 template <int NT>
 moe_b200_status route_noalloc_launch(int dev, const void* t, int t_dtype, int T, int H,
                                      const uint16_t* w, const float* b, int E, int K, int* topk_i,
                                      float* topk_w, int* counts, int* offsets, cudaStream_t st) {
     const size_t smem = route_small_smem_bytes(H);
-    const int bit = NT == 1 ? 1 : NT == 2 ? 2 : NT == 4 ? 4 : 8;
-    if (!(g_na_attr_done[dev] & bit)) {
-        CU_TRY(nullptr, cudaFuncSetAttribute(route_small_kernel<NT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)route_small_smem_bytes(MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN)));
-        g_na_attr_done[dev] |= bit;
-    }
+    static_assert((size_t)(RBS + RGE) * MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN * 2 + 256 * sizeof(int) <=
+                      ROUTE_SMALL_SMEM_LIMIT,
+                  "the largest hidden size of the allocation-free entry point must fit the shared limit");
+    CU_TRY(nullptr, ensure_route_small_attr<NT>(dev));
     int* scratch = g_na_scratch_ptr[dev];
     int* blk_hist = scratch;
     int* blk_base = scratch + NA_HIST_INTS;
@@ -1158,7 +1228,7 @@ moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local
 
 }  // extern "C"
 
-#ifdef TC5_TRACE
+#if defined(MOE_B200_TEST_AIDS) && defined(TC5_TRACE)
 // Debug builds only (not declared in the header): reads the hand-off timestamps.
 extern "C" int moe_b200_debug_trace_read(long long* out, int n) {
     cudaDeviceSynchronize();

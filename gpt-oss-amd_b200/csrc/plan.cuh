@@ -19,12 +19,12 @@ namespace moe {
 
 // One block.  blk_hist [nblk, E] -> cnt[E], off[E+1] (rows sorted by expert),
 // blk_base[nblk, E] (first row of block b's assignments to expert e), and the
-// GEMM tile table tile_start[E+1] = prefix of ceil(cnt/bn).
-// Also clears counters the later kernels use.
-__global__ void __launch_bounds__(256)
-plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __restrict__ cnt,
-            int* __restrict__ off, int* __restrict__ tile_start, int* __restrict__ blk_base) {
-    __shared__ int s_cnt[256];
+// GEMM tile table tile_start[E+1] = prefix of ceil(cnt/bn).  s_cnt[256] (shared)
+// holds the counts for every thread when the function returns.
+__device__ __forceinline__ void plan_body(const int* __restrict__ blk_hist, int nblk, int E, int bn,
+                                          int* __restrict__ cnt, int* __restrict__ off,
+                                          int* __restrict__ tile_start, int* __restrict__ blk_base,
+                                          int* s_cnt) {
     __shared__ int s_off[257];
     const int e = threadIdx.x;
     int total = 0;
@@ -56,6 +56,14 @@ plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __re
             run += blk_hist[(size_t)b * E + e];
         }
     }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(256)
+plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __restrict__ cnt,
+            int* __restrict__ off, int* __restrict__ tile_start, int* __restrict__ blk_base) {
+    __shared__ int s_cnt[256];
+    plan_body(blk_hist, nblk, E, bn, cnt, off, tile_start, blk_base, s_cnt);
 }
 
 // Stable placement of every (token, k) assignment into its expert's row range
@@ -127,10 +135,37 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
 
 // out[t,:] (+)= sum over the token's K assignments, ascending expert index, of
 // topk_w * y[slot,:].  One block per token.
+// Expert-parallel peer mode: `wait_flags` points at this rank's G "results
+// delivered" flags; the block first waits (bounded) until every rank has stored
+// its result rows into y.  The grid then has at least one block even for T == 0:
+// the wait is also what keeps this rank from starting the next call while a peer
+// still reads what this call sent it.
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ y, int T, int H, int K, const int* __restrict__ topk_i,
                const float* __restrict__ topk_w, const int* __restrict__ slot_of,
-               float* __restrict__ out, int accumulate) {
+               float* __restrict__ out, int accumulate, const int* __restrict__ wait_flags, int G,
+               int seq, int* __restrict__ status) {
+    if (wait_flags) {
+        if ((int)threadIdx.x < G) {
+            const volatile int* f = wait_flags + threadIdx.x;
+            unsigned long long t_start = 0;
+            while ((int)(*f - seq) < 0) {
+                if (*reinterpret_cast<volatile int*>(status) != 0)
+                    break;
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t_start == 0)
+                    t_start = now;
+                else if (now - t_start > 2000000000ull) {
+                    report_status(status, 0x301);  // peer::DS_TIMEOUT_PEER
+                    break;
+                }
+                __nanosleep(100);
+            }
+            __threadfence_system();
+        }
+        __syncthreads();
+    }
     const int t = blockIdx.x;
     if (t >= T)
         return;

@@ -1,4 +1,4 @@
-// PTX wrappers shared by the tcgen05 expert GEMMs (gemm_tc5.cuh, gemm_tc5_swap.cuh):
+// PTX wrappers shared by the tcgen05 expert GEMMs (gemm_tc5_pair.cuh, gemm_tc5_swap.cuh):
 // mbarrier, TMA / bulk copies, tensor-memory allocation, tcgen05.mma / commit / ld,
 // shared-memory and instruction descriptors, bounded waits.
 #pragma once
@@ -101,6 +101,12 @@ __device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Orders earlier generic-proxy accesses to global memory (here: rows that another
+// GPU stored and this thread has just seen flagged) before later async-proxy ones
+// (TMA loads) of this thread.
+__device__ __forceinline__ void fence_proxy_async_global() {
+    asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -217,8 +223,9 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
 }
 
 
-#ifdef TC5_TRACE
-// Debug builds only (-DTC5_TRACE=<MODE>): SM-clock timestamps of the pipeline hand-offs of CTA 0.
+#if defined(MOE_B200_TEST_AIDS) && defined(TC5_TRACE)
+// Test-aids builds only (-DMOE_B200_TEST_AIDS -DTC5_TRACE=<MODE>): SM-clock timestamps of the
+// pipeline hand-offs of CTA 0.
 constexpr int TRACE_STEPS = 512, TRACE_SLOTS = 16;
 __device__ long long g_trace[TRACE_STEPS * TRACE_SLOTS];
 #define TRACE(step, slot)                                                   \

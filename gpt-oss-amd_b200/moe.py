@@ -44,14 +44,17 @@ class MoEEngine:
         self.first_expert, self.n_local = capi.shard_range(shape.n_experts, ep_size, ep_rank)
         cfg = capi.Config(shape.hidden, shape.intermediate, shape.n_experts, shape.top_k, n_layers,
                           shape.alpha, shape.limit, max_tokens, ep_rank, ep_size, device, gemm_impl)
+        # a handle belongs to the library that created it: the shipped one, or (for the
+        # cross-check GEMM of the parity tests) its test-aids build
+        self._lib = capi.lib(test_aids=(gemm_impl != capi.GEMM_TCGEN05))
         h = ctypes.c_void_p()
-        capi.check(capi.lib().moe_b200_create(ctypes.byref(cfg), ctypes.byref(h)))
+        capi.check(self._lib.moe_b200_create(ctypes.byref(cfg), ctypes.byref(h)), None, self._lib)
         self._h = h
 
     # -- lifetime ---------------------------------------------------------
     def close(self):
         if getattr(self, "_h", None):
-            capi.lib().moe_b200_destroy(self._h)
+            self._lib.moe_b200_destroy(self._h)
             self._h = None
 
     def __del__(self):
@@ -68,15 +71,15 @@ class MoEEngine:
 
     # -- weights ----------------------------------------------------------
     def set_router(self, layer: int, w_bf16_bits, bias):
-        capi.check(capi.lib().moe_b200_set_router(self._h, layer, _ptr(w_bf16_bits), _ptr(bias)),
-                   self._h)
+        capi.check(self._lib.moe_b200_set_router(self._h, layer, _ptr(w_bf16_bits), _ptr(bias)),
+                   self._h, self._lib)
 
     def set_experts(self, layer: int, first_expert: int, blocks1, scales1, bias1, blocks2, scales2,
                     bias2):
         n = blocks1.shape[0]
-        capi.check(capi.lib().moe_b200_set_experts_mxfp4(
+        capi.check(self._lib.moe_b200_set_experts_mxfp4(
             self._h, layer, first_expert, n, _ptr(blocks1), _ptr(scales1), _ptr(bias1),
-            _ptr(blocks2), _ptr(scales2), _ptr(bias2)), self._h)
+            _ptr(blocks2), _ptr(scales2), _ptr(bias2)), self._h, self._lib)
 
     def load_layer(self, layer: int, lw: LayerWeights):
         """Router plus the part of this rank's contiguous expert shard that
@@ -107,9 +110,9 @@ class MoEEngine:
             ti = torch.empty(T, self.shape.top_k, dtype=torch.int32, device=t.device)
             tw = torch.empty(T, self.shape.top_k, dtype=torch.float32, device=t.device)
         s = stream if stream is not None else torch.cuda.current_stream(t.device)
-        capi.check(capi.lib().moe_b200_forward(
+        capi.check(self._lib.moe_b200_forward(
             self._h, layer, _ptr(t.contiguous()), dt, T, _ptr(out), int(accumulate), _ptr(sc),
-            _ptr(ti), _ptr(tw), ctypes.c_void_p(s.cuda_stream)), self._h)
+            _ptr(ti), _ptr(tw), ctypes.c_void_p(s.cuda_stream)), self._h, self._lib)
         return (out, sc, ti, tw) if side else out
 
     def forward_host(self, layer: int, t_host, out_host, topk_i_host=None, topk_w_host=None):
@@ -119,9 +122,9 @@ class MoEEngine:
             dt = capi.DTYPE_BF16 if t_host.dtype == torch.bfloat16 else capi.DTYPE_F32
         else:
             dt = capi.DTYPE_BF16 if t_host.dtype == np.uint16 else capi.DTYPE_F32
-        capi.check(capi.lib().moe_b200_forward_host(
+        capi.check(self._lib.moe_b200_forward_host(
             self._h, layer, _ptr(t_host), dt, T, _ptr(out_host), _ptr(topk_i_host),
-            _ptr(topk_w_host)), self._h)
+            _ptr(topk_w_host)), self._h, self._lib)
         return out_host
 
     # -- expert parallel ----------------------------------------------------
@@ -132,17 +135,23 @@ class MoEEngine:
         return buf.raw
 
     def ep_init(self, unique_id: bytes):
-        capi.check(capi.lib().moe_b200_ep_init(self._h, unique_id), self._h)
+        capi.check(self._lib.moe_b200_ep_init(self._h, unique_id), self._h, self._lib)
 
     def ep_peer_export(self) -> bytes:
         buf = ctypes.create_string_buffer(capi.EP_PEER_EXPORT_BYTES)
-        capi.check(capi.lib().moe_b200_ep_peer_export(self._h, buf), self._h)
+        capi.check(self._lib.moe_b200_ep_peer_export(self._h, buf), self._h, self._lib)
         return buf.raw
 
     def ep_peer_enable(self, blobs_in_rank_order: list[bytes]):
         """Map the peers' exchange buffers: the exchange then runs inside the
         kernels over NVLink peer memory instead of NCCL."""
-        capi.check(capi.lib().moe_b200_ep_peer_enable(self._h, b"".join(blobs_in_rank_order)), self._h)
+        capi.check(self._lib.moe_b200_ep_peer_enable(self._h, b"".join(blobs_in_rank_order)), self._h, self._lib)
+
+    def ep_peer_sequence(self) -> int:
+        return int(self._lib.moe_b200_ep_peer_sequence(self._h))
+
+    def ep_peer_resync(self, sequence: int):
+        capi.check(self._lib.moe_b200_ep_peer_resync(self._h, int(sequence)), self._h, self._lib)
 
     def ep_connect(self, dist, mode: str = "peer"):
         """Collective over the torch.distributed process group ``dist`` (any
@@ -159,20 +168,20 @@ class MoEEngine:
     # -- introspection ------------------------------------------------------
     def device_status(self) -> int:
         w = ctypes.c_int()
-        st = capi.lib().moe_b200_device_status(self._h, ctypes.byref(w))
+        st = self._lib.moe_b200_device_status(self._h, ctypes.byref(w))
         if st not in (capi.OK, capi.ERR_DEVICE):
-            capi.check(st, self._h)
+            capi.check(st, self._h, self._lib)
         return w.value
 
     def device_bytes(self) -> int:
-        return int(capi.lib().moe_b200_device_bytes(self._h))
+        return int(self._lib.moe_b200_device_bytes(self._h))
 
     def last_launch_count(self) -> int:
-        return int(capi.lib().moe_b200_last_launch_count(self._h))
+        return int(self._lib.moe_b200_last_launch_count(self._h))
 
     def last_expert_counts(self) -> list[int]:
         arr = (ctypes.c_int * self.n_local)()
-        capi.check(capi.lib().moe_b200_last_expert_counts(self._h, arr), self._h)
+        capi.check(self._lib.moe_b200_last_expert_counts(self._h, arr), self._h, self._lib)
         return list(arr)
 
     def last_intermediate(self, n_tokens: int) -> torch.Tensor:
@@ -181,19 +190,19 @@ class MoEEngine:
         K, I = self.shape.top_k, self.shape.intermediate
         out = torch.empty(n_tokens, K, I, dtype=torch.int16, device=f"cuda:{self.device}")
         s = torch.cuda.current_stream(out.device)
-        capi.check(capi.lib().moe_b200_last_intermediate(self._h, n_tokens, _ptr(out),
-                                                         ctypes.c_void_p(s.cuda_stream)), self._h)
+        capi.check(self._lib.moe_b200_last_intermediate(self._h, n_tokens, _ptr(out),
+                                                         ctypes.c_void_p(s.cuda_stream)), self._h, self._lib)
         return out
 
     def profile(self, n_calls: int):
         """Arm per-stage CUDA-event timing for the next n_calls forwards."""
-        capi.check(capi.lib().moe_b200_profile(self._h, n_calls), self._h)
+        capi.check(self._lib.moe_b200_profile(self._h, n_calls), self._h, self._lib)
 
     def profile_read(self, call: int) -> dict:
         """Stage name -> milliseconds of the call-th profiled forward (after a
         synchronise of the stream it ran on)."""
         ms = (ctypes.c_float * capi.N_STAGES)()
-        capi.check(capi.lib().moe_b200_profile_read(self._h, call, ms), self._h)
+        capi.check(self._lib.moe_b200_profile_read(self._h, call, ms), self._h, self._lib)
         return dict(zip(capi.STAGE_NAMES, (float(v) for v in ms)))
 
     def unpack_resident(self, layer: int, local_expert: int, which: int) -> torch.Tensor:
@@ -201,8 +210,8 @@ class MoEEngine:
         shape = (2 * I, H) if which == 1 else (H, I)
         out = torch.empty(shape, dtype=torch.int16, device=f"cuda:{self.device}")
         s = torch.cuda.current_stream(out.device)
-        capi.check(capi.lib().moe_b200_unpack_resident(self._h, layer, local_expert, which, _ptr(out),
-                                                       ctypes.c_void_p(s.cuda_stream)), self._h)
+        capi.check(self._lib.moe_b200_unpack_resident(self._h, layer, local_expert, which, _ptr(out),
+                                                       ctypes.c_void_p(s.cuda_stream)), self._h, self._lib)
         return out
 
 

@@ -53,13 +53,17 @@ typedef enum {
 #define MOE_B200_DTYPE_F32 0  /* the engine's s->t buffer (include/model.hpp:113) */
 #define MOE_B200_DTYPE_BF16 1 /* already-rounded activations                      */
 
-/* Expert GEMM implementations.  TCGEN05 is the product path (large batches run
- * on CTA pairs, tcgen05.mma.cta_group::2); MMA_SYNC is a plain warp-MMA kernel
- * kept to cross-check it on the device; TCGEN05_1CTA runs large batches on the
- * single-CTA tcgen05 kernel (for comparison). */
+/* The expert GEMMs are tcgen05 kernels (CTA pairs for large batches, token rows
+ * on the accumulator lanes for small ones); moe_b200_config.gemm_impl must be
+ * MOE_B200_GEMM_TCGEN05 (= 0). */
 #define MOE_B200_GEMM_TCGEN05 0
+#ifdef MOE_B200_TEST_AIDS
+/* Test-aids build of the library only (compiled with -DMOE_B200_TEST_AIDS, never
+ * shipped): a plain warp-MMA kernel with the same inputs, layout and rounding
+ * points, used by the parity tests to cross-check the tcgen05 kernels on the
+ * device at sizes the CPU oracle cannot reach. */
 #define MOE_B200_GEMM_MMA_SYNC 1
-#define MOE_B200_GEMM_TCGEN05_1CTA 2
+#endif
 
 /* Mirrors the MoE-related fields of OssConfig (include/model.hpp:25-48) plus
  * the expert-parallel placement of OssTransformerHybrid (include/model.hpp:
@@ -72,11 +76,12 @@ typedef struct {
     int n_layers;          /* layers held by this handle                       */
     float swiglu_alpha;    /* 1.702 in the reference (src/run.cpp:673)         */
     float swiglu_limit;    /* OssConfig.swiglu_limit                           */
-    int max_tokens;        /* OssConfig.batch_size: most tokens per call, per rank */
+    int max_tokens;        /* OssConfig.batch_size: most tokens per call, per rank;
+                              with ep_size > 1 the same value on every rank      */
     int ep_rank;           /* this GPU's shard, 0 <= ep_rank < ep_size         */
     int ep_size;           /* 1 = all experts local                            */
     int device;            /* CUDA device ordinal                              */
-    int gemm_impl;         /* MOE_B200_GEMM_*                                  */
+    int gemm_impl;         /* MOE_B200_GEMM_TCGEN05                            */
 } moe_b200_config;
 
 /* Contiguous expert shard of a rank, remainder to the low ranks: the rule of
@@ -147,17 +152,29 @@ moe_b200_status moe_b200_ep_init(moe_b200_handle h, const char id[128]);
 
 /* Peer-memory mode of the expert-parallel exchange (optional, instead of
  * moe_b200_ep_init): the ranks map each other's exchange buffers (CUDA IPC over
- * NVLink) and the exchange happens inside the permute kernel and the down
- * GEMM's epilogue -- no NCCL call, no host wait.  Every rank calls
+ * NVLink) and the exchange happens inside the plan / permute kernels, the expert
+ * GEMMs and the combine kernel -- no NCCL call, no host wait, no extra launch.  Every rank calls
  * moe_b200_ep_peer_export, the ranks exchange the blobs by any host channel, and
  * every rank passes all of them, in rank order, to moe_b200_ep_peer_enable.  All
- * ranks must be processes on one node whose GPUs have peer access.  (The
+ * ranks must be processes on one node whose GPUs have peer access, created with
+ * the same hidden_dim, n_experts, experts_per_token, max_tokens and ep_size: the
+ * blobs carry these and a mismatch is refused with MOE_B200_ERR_INVALID before
+ * anything is mapped (peers store into each other's buffers at addresses they
+ * compute from their own configuration).  (The
  * reference enables peer access between all pairs at start-up too,
  * src/getp/run.cpp:186-202.) */
 #define MOE_B200_EP_IPC_BYTES 64
 #define MOE_B200_EP_PEER_EXPORT_BYTES (4 * MOE_B200_EP_IPC_BYTES)
 moe_b200_status moe_b200_ep_peer_export(moe_b200_handle h, char* blob_out);
 moe_b200_status moe_b200_ep_peer_enable(moe_b200_handle h, const char* all_blobs);
+
+/* Call counter of the peer-memory exchange on this rank (the value its flags
+ * carry), and the way to re-align the ranks after a call that some of them did
+ * not make: every rank passes the same `sequence`, at least as large as every
+ * rank's current counter, with no call in flight.  (The reference has no
+ * recovery path: a failed peer copy exits the process, include/model.hpp:8-17.) */
+int moe_b200_ep_peer_sequence(moe_b200_handle h);
+moe_b200_status moe_b200_ep_peer_resync(moe_b200_handle h, int sequence);
 
 /* The host-side plan of one expert-parallel exchange, as moe_b200_forward
  * computes it: cnt_all [ep_size, n_experts] holds every rank's per-expert row
@@ -173,11 +190,17 @@ size_t moe_b200_device_bytes(moe_b200_handle h);
 /* Text of the last error on this handle (or of the last failed create when h
  * is NULL).  Never NULL. */
 const char* moe_b200_last_error(moe_b200_handle h);
-/* Reads the device status word (synchronises the device): 0 = no kernel has
- * reported a problem; otherwise a code naming the wait that ran out (0x101..
- * 0x106: a pipeline barrier of an expert GEMM; 0x201 / 0x202: a scale byte or
- * expert index out of range; 0x301: a peer's flag in the peer-memory exchange,
- * i.e. a rank that did not join the call within 2 s).  The context stays usable. */
+/* Reads AND CLEARS the device status word (synchronises the device): 0 = no
+ * kernel has reported a problem since the last read; otherwise the code of the
+ * first problem (0x101..0x106: a pipeline barrier of an expert GEMM timed out;
+ * 0x202: an expert index out of range; 0x301: a peer's flag in the peer-memory
+ * exchange, i.e. a rank that did not join the call within 2 s; 0x302: the
+ * ranks' row counts would overflow a receive buffer) and MOE_B200_ERR_DEVICE.
+ * The CUDA context stays usable.  After 0x301 / 0x302 the output of that call is
+ * undefined and the ranks' call counters may differ: before the next
+ * expert-parallel call every rank reads its status, the ranks agree on the
+ * largest moe_b200_ep_peer_sequence() over any host channel, and each passes it
+ * to moe_b200_ep_peer_resync(). */
 moe_b200_status moe_b200_device_status(moe_b200_handle h, int* status_word);
 /* Number of kernels the last moe_b200_forward launched on this handle. */
 int moe_b200_last_launch_count(moe_b200_handle h);
@@ -202,7 +225,9 @@ moe_b200_status moe_b200_last_expert_counts(moe_b200_handle h, int* counts);
 #define MOE_B200_STAGE_GEMM2 6    /* down GEMM                               */
 #define MOE_B200_STAGE_RETURN 7   /* result all-to-all (EP)                  */
 #define MOE_B200_STAGE_COMBINE 8  /* routing-weighted combine                */
-#define MOE_B200_N_STAGES 9
+#define MOE_B200_STAGE_H2D 9      /* moe_b200_forward_host: activations in   */
+#define MOE_B200_STAGE_D2H 10     /* moe_b200_forward_host: result out       */
+#define MOE_B200_N_STAGES 11
 moe_b200_status moe_b200_profile(moe_b200_handle h, int n_calls);
 moe_b200_status moe_b200_profile_read(moe_b200_handle h, int call, float* ms);
 

@@ -375,3 +375,15 @@ int oracle_num_threads(void) {
     return 1;
 #endif
 }
+
+/* OpenMP threads of the calling thread's later parallel regions, whatever
+ * OMP_NUM_THREADS the process inherited (the reference's run.sh sets its own
+ * count the same way, run.sh:6). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -77,6 +77,25 @@ def num_threads(impl: str = "port") -> int:
     return int(_lib_ref().ref_num_threads() if impl == "reference" else _lib_port().oracle_num_threads())
 
 
+def host_cores() -> int:
+    """Cores this process may run on (the affinity mask, not OMP_NUM_THREADS)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def use_all_cores() -> int:
+    """Make both checkers use every core this process may run on, whatever
+    OMP_NUM_THREADS the launcher exported (torch.distributed.run exports 1).
+    Returns the thread count set."""
+    n = host_cores()
+    _lib_port().oracle_set_num_threads(n)
+    if have_reference():
+        _lib_ref().ref_set_num_threads(n)
+    return n
+
+
 # ---------------------------------------------------------------------------
 # MXFP4
 

@@ -24,6 +24,12 @@ void ref_matmul(float* xout, float* x, float* w, int n, int d) { matmul(xout, x,
 void ref_softmax(float* x, int size) { softmax(x, size); }
 void ref_topk(float* v, int* i, float* score, int E, int K) { topk(v, i, score, E, K); }
 int ref_num_threads(void) { return omp_get_max_threads(); }
+// Threads of the calling thread's later parallel regions, whatever OMP_NUM_THREADS
+// the process inherited.
+void ref_set_num_threads(int n) {
+    if (n > 0)
+        omp_set_num_threads(n);
+}
 
 // The MoE block of the reference forward() (src/run.cpp:628-707) for T tokens,
 // token at a time, experts in index order.  Only the ~40 lines of glue between

@@ -133,10 +133,16 @@ def cpu_worker(rank, world, port, shape_kw, T, seed, outdir):
 # over NCCL (mode "nccl") or over peer memory (mode "peer").
 
 
-def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl, mode):
+def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl, mode, sample=0):
+    """One rank of an expert-parallel run.  With ``sample`` > 0 (full-size layers) the
+    rank itself checks that many of its own tokens against the CPU oracle -- experts
+    are regenerated from the seed, whichever rank holds them -- and saves the figures."""
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import json
+
     import gpt_oss_amd_b200 as pkg
     from gpt_oss_amd_b200 import synth
+    from oracle import parity
 
     _init(rank, world, port)
     torch.cuda.set_device(rank)
@@ -157,20 +163,32 @@ def gpu_worker(rank, world, port, shape_kw, T, seed, outdir, gemm_impl, mode):
     t2 = t if rank != world - 1 else t[:0]
     out2 = eng.forward(0, t2)
     torch.cuda.synchronize()
+    # third call: everybody again (the call after a rank had nothing to send)
+    out3 = eng.forward(0, t)
+    torch.cuda.synchronize()
     status = eng.device_status()
+    figures = {}
+    if sample > 0 and Tl > 0:
+        rows = np.unique(np.linspace(0, Tl - 1, sample).astype(np.int64))
+        res = {"out": out.cpu().numpy()[rows], "topk_i": ti.cpu().numpy()[rows],
+               "topk_w": tw.cpu().numpy()[rows]}
+        figures = parity.compare_sampled(res, x_bits[rows], lw.w_router, lw.b_router,
+                                         lambda e: synth.make_experts(shape, seed, e, 1), shape.top_k)
     np.savez(os.path.join(outdir, f"gpu_rank{rank}.npz"), out=out.cpu().numpy(),
              topk_i=ti.cpu().numpy(), topk_w=tw.cpu().numpy(), out2=out2.cpu().numpy(),
-             start=starts[rank], status=status, counts=np.array(counts))
+             out3=out3.cpu().numpy(), start=starts[rank], status=status, counts=np.array(counts),
+             figures=json.dumps(figures), device_bytes=eng.device_bytes())
     dist.barrier()
     eng.close()
     dist.destroy_process_group()
 
 
 def gpu_missing_rank_worker(rank, world, port, shape_kw, T, seed, outdir):
-    """Failure detection without a GPU fault: rank 1 never joins the call.  Rank 0's
-    peer-flag waits run out (2 s each), its kernels return, the status word names the
+    """Failure detection without a GPU fault: rank 1 never joins the first call.  Rank
+    0's peer-flag waits run out (2 s), its kernels return, the status word names the
     wait and the context stays usable.  Rank 1 stays alive (its buffers stay mapped)
-    until rank 0 has read the status."""
+    until rank 0 has read the status.  Then the ranks agree on a sequence number over
+    the host channel, resynchronise, and make a call together that must be right."""
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import gpt_oss_amd_b200 as pkg
     from gpt_oss_amd_b200 import synth
@@ -178,21 +196,33 @@ def gpu_missing_rank_worker(rank, world, port, shape_kw, T, seed, outdir):
     _init(rank, world, port)
     torch.cuda.set_device(rank)
     shape = pkg.MoEShape(**shape_kw)
+    starts = split_tokens(T, world)
     eng = pkg.MoEEngine(shape, max_tokens=T, ep_rank=rank, ep_size=world, device=rank)
     eng.ep_connect(dist, "peer")
     lw = synth.make_layer(shape, seed, first=eng.first_expert, n=eng.n_local)
     eng.load_layer(0, lw)
     dist.barrier()
+    x_all = synth.make_tokens(T, shape.hidden, seed)
+    x_bits = x_all[starts[rank]:starts[rank + 1]]
+    t = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).cuda().view(torch.bfloat16)
     status, usable = 0, True
     if rank == 0:
-        x_bits = synth.make_tokens(T, shape.hidden, seed)
-        t = torch.from_numpy(np.ascontiguousarray(x_bits).view(np.int16)).cuda().view(torch.bfloat16)
         eng.forward(0, t)
         torch.cuda.synchronize()
-        status = eng.device_status()
+        status = eng.device_status()  # reads and clears
         # the context still works
         usable = bool((torch.ones(8, device="cuda") * 2).sum().item() == 16.0)
-    np.savez(os.path.join(outdir, f"miss_rank{rank}.npz"), status=status, usable=usable)
-    dist.barrier()  # rank 1 leaves only after rank 0 is done, nothing in flight
+    dist.barrier()  # nothing is in flight on either rank here
+    seqs = [None] * world
+    dist.all_gather_object(seqs, eng.ep_peer_sequence())
+    eng.ep_peer_resync(max(seqs))
+    dist.barrier()
+    out, _, ti, tw = eng.forward(0, t, side=True)
+    torch.cuda.synchronize()
+    status_after = eng.device_status()
+    np.savez(os.path.join(outdir, f"miss_rank{rank}.npz"), status=status, usable=usable,
+             status_after=status_after, seqs=np.array(seqs), out=out.cpu().numpy(),
+             topk_i=ti.cpu().numpy(), topk_w=tw.cpu().numpy())
+    dist.barrier()  # a rank leaves only after the other is done, nothing in flight
     eng.close()
     dist.destroy_process_group()

@@ -70,7 +70,7 @@ def test_create_rejects_bad_configs():
     L = capi.lib()
     h = ctypes.c_void_p()
     for kw in [dict(hidden_dim=100), dict(n_experts=300), dict(experts_per_token=9),
-               dict(ep_size=2, ep_rank=2), dict(max_tokens=0), dict(gemm_impl=5)]:
+               dict(ep_size=2, ep_rank=2), dict(max_tokens=0), dict(gemm_impl=5), dict(gemm_impl=1)]:
         base = dict(hidden_dim=128, intermediate_dim=64, n_experts=8, experts_per_token=4,
                     n_layers=1, swiglu_alpha=1.702, swiglu_limit=7.0, max_tokens=16, ep_rank=0,
                     ep_size=1, device=0, gemm_impl=0)
@@ -78,6 +78,43 @@ def test_create_rejects_bad_configs():
         cfg = capi.Config(**base)
         assert L.moe_b200_create(ctypes.byref(cfg), ctypes.byref(h)) == capi.ERR_INVALID, kw
         assert L.moe_b200_last_error(None)
+
+
+def test_test_aids_build_is_separate_from_the_shipped_library():
+    """The cross-check GEMM exists only in the test-aids build: the shipped library
+    refuses gemm_impl = 1 (checked above); the test-aids build gets past the argument
+    checks with it and, on a machine without a GPU, stops at the missing device."""
+    L = capi.lib(test_aids=True)
+    assert b"test-aids" in L.moe_b200_version()
+    assert b"test-aids" not in capi.lib().moe_b200_version()
+    for name in capi.SYMBOLS:
+        assert hasattr(L, name), name
+    if not torch.cuda.is_available():
+        cfg = capi.Config(hidden_dim=128, intermediate_dim=64, n_experts=8, experts_per_token=4,
+                          n_layers=1, swiglu_alpha=1.702, swiglu_limit=7.0, max_tokens=16, ep_rank=0,
+                          ep_size=1, device=0, gemm_impl=capi.GEMM_MMA_SYNC)
+        h = ctypes.c_void_p()
+        assert L.moe_b200_create(ctypes.byref(cfg), ctypes.byref(h)) == capi.ERR_NO_DEVICE
+
+
+def test_header_compiles_as_c99_and_links(tmp_path):
+    """tests/c_abi_smoke.c is the engine-side binding as code: a plain-C translation
+    unit that includes include/moe_b200.h, compiled with -std=c99 -Wall -Werror and
+    linked against the shipped library.  It runs the pure-host entry points and, on a
+    machine without a GPU, checks that create fails with MOE_B200_ERR_NO_DEVICE."""
+    import subprocess
+
+    exe = tmp_path / "c_abi_smoke"
+    lib_dir = os.path.dirname(capi.LIB_PATH)
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic",
+                    "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "c_abi_smoke.c"),
+                    "-L", lib_dir, "-l:libmoe_b200.so", f"-Wl,-rpath,{lib_dir}", "-o", str(exe)],
+                   check=True, capture_output=True, text=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "c_abi_smoke ok" in res.stdout
+    if not torch.cuda.is_available():
+        assert "no device" in res.stdout
 
 
 def test_retile_word_roundtrip_semantics():

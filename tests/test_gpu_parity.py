@@ -13,12 +13,12 @@ import torch
 import gpt_oss_amd_b200 as pkg
 from gpt_oss_amd_b200 import capi, synth
 from oracle import oracle
-from parity_util import compare, oracle_case, run_gpu
+from parity_util import compare, compare_sampled, oracle_case, run_gpu
 
 pytestmark = pytest.mark.gpu
 
-IMPLS = [pytest.param(capi.GEMM_MMA_SYNC, id="mma_sync"), pytest.param(capi.GEMM_TCGEN05, id="tcgen05"),
-         pytest.param(capi.GEMM_TCGEN05_1CTA, id="tcgen05_1cta")]
+# GEMM_MMA_SYNC is the plain warp-MMA cross-check kernel of the test-aids build
+IMPLS = [pytest.param(capi.GEMM_MMA_SYNC, id="mma_sync"), pytest.param(capi.GEMM_TCGEN05, id="tcgen05")]
 
 
 def _bits(t):
@@ -115,6 +115,8 @@ CASES = [
     (128, 64, 32, 4, 2500),   # above the small-batch routing threshold
     (128, 64, 128, 4, 2100),
     (320, 192, 4, 2, 700),    # large-batch GEMM kernel with partial weight tiles
+    (128, 64, 128, 4, 4000),  # large-batch (CTA-pair) GEMM kernel with 128 experts, 125 rows each
+    (192, 128, 128, 4, 9000), # the same above 256 rows per expert: several token tiles per expert
 ]
 
 
@@ -126,7 +128,7 @@ def test_block_matches_oracle(H, I, E, K, T, impl):
     x_bits = synth.make_tokens(T, H, seed=T)
     ref = oracle_case(lw, x_bits)
     res = run_gpu(shape, lw, x_bits, impl)
-    compare(res, ref, K, f"{(H, I, E, K, T)}")
+    print((H, I, E, K, T), compare(res, ref, K, f"{(H, I, E, K, T)}"))
     assert sum(res["counts"]) == T * K
     hist = np.bincount(ref["topk_i"].reshape(-1), minlength=E)
     assert list(hist) == res["counts"]
@@ -186,9 +188,133 @@ def test_tcgen05_equals_mma_sync_at_prefill_size():
     assert np.linalg.norm(d) / np.linalg.norm(a["out"].astype(np.float64)) < 5e-4
     assert max(a["counts"]) > 2 * (T * 4 / 32)  # the skew is real
     sample = np.arange(0, T, T // 16)
-    ref = oracle_case(lw, x_bits[sample])
     sub = {k: b[k][sample] for k in ("out", "topk_i", "topk_w", "h_bits")}
-    print("prefill sample", compare(sub, ref, 4, "prefill sample"))
+    print("prefill sample", compare_sampled(sub, lw, x_bits[sample], lw.w_router, lw.b_router, 4,
+                                            "prefill sample"))
+
+
+def _sample_rows(T, n, seed):
+    """n distinct token rows of a batch of T: the first and last rows (tile edges)
+    plus a seeded draw from the rest."""
+    rng = np.random.default_rng(seed)
+    mid = rng.choice(np.arange(1, T - 1), size=n - 2, replace=False)
+    return np.sort(np.concatenate([[0, T - 1], mid]))
+
+
+def test_config3_headline_shape_sampled():
+    """The benchmarked configuration itself: gpt-oss-120b-shaped layer, E = 128,
+    H = I = 2880, 16384 tokens, uniform routing -- the CTA-pair GEMM with 128-expert
+    tile tables and several token tiles per expert.  All 16384 tokens run on the GPU;
+    a 32-token sample goes through the CPU oracle (which decodes only the experts
+    those tokens touch) with the full rule set, h-flip accounting included."""
+    shape = pkg.MoEShape(n_experts=128)
+    T = 16384
+    lw = synth.make_layer(shape, seed=0)
+    x_bits = synth.make_tokens(T, shape.hidden, seed=0)
+    res = run_gpu(shape, lw, x_bits, capi.GEMM_TCGEN05)
+    assert sum(res["counts"]) == T * 4
+    assert min(res["counts"]) > 256  # every expert has more than one token tile
+    sample = _sample_rows(T, 32, seed=3)
+    sub = {k: res[k][sample] for k in ("out", "topk_i", "topk_w", "h_bits")}
+    m = compare_sampled(sub, lw, x_bits[sample], lw.w_router, lw.b_router, 4, "config 3 sample")
+    print("config3", m)
+    # and every token against the cross-check GEMM (same rounding points, other summation order)
+    x = run_gpu(shape, lw, x_bits, capi.GEMM_MMA_SYNC, want_h=False)
+    assert np.array_equal(x["topk_i"], res["topk_i"])
+    d = x["out"].astype(np.float64) - res["out"].astype(np.float64)
+    rel = np.linalg.norm(d) / np.linalg.norm(x["out"].astype(np.float64))
+    print("config3 tcgen05 vs mma_sync: rel-L2", rel, "max-abs", np.abs(d).max())
+    assert rel < 5e-4
+    # the router at this size is the tensor-core kernel: all 16384 index rows against the oracle
+    scores, ti, _ = oracle.route(synth.bf16_bits_to_f32(x_bits), synth.bf16_bits_to_f32(lw.w_router),
+                                 lw.b_router, 4, round_mode=1)
+    from parity_util import tie_mask
+    ok = ~tie_mask(scores, 4)
+    assert int((res["topk_i"][ok] != ti[ok]).any(axis=1).sum()) == 0
+    assert list(np.bincount(ti.reshape(-1), minlength=128)) == res["counts"] or (~ok).any()
+
+
+def test_config2_zipf_prefill_sampled():
+    """gpt-oss-20b-shaped layer, 8192 tokens, Zipf(1.1) router bias scaled so that the
+    busiest expert draws about 4x the mean load (the skewed configuration): the
+    grouped GEMM with tiles from 1 to ~17 per expert.  32-token oracle sample."""
+    shape = pkg.MoEShape()
+    T = 8192
+    lw = synth.make_layer(shape, seed=0, zipf_s=1.1, zipf_gain=synth.ZIPF_GAIN_4X)
+    x_bits = synth.make_tokens(T, shape.hidden, seed=0)
+    res = run_gpu(shape, lw, x_bits, capi.GEMM_TCGEN05)
+    skew = max(res["counts"]) / (sum(res["counts"]) / len(res["counts"]))
+    assert 3.5 < skew < 4.5, skew
+    sample = _sample_rows(T, 32, seed=5)
+    sub = {k: res[k][sample] for k in ("out", "topk_i", "topk_w", "h_bits")}
+    m = compare_sampled(sub, lw, x_bits[sample], lw.w_router, lw.b_router, 4, "config 2 sample")
+    print("config2 skew", skew, m)
+
+
+def test_config1_decode_batch_three_layers():
+    """The decode-shaped configuration: 256 tokens per step through stacked
+    gpt-oss-20b-shaped layers with independent seeds (three of the 24), 32 rows per
+    expert -- the small-batch GEMM.  Every token of every layer against the oracle."""
+    shape = pkg.MoEShape()
+    T, layers = 256, 3
+    x_bits = synth.make_tokens(T, shape.hidden, seed=0)
+    with pkg.MoEEngine(shape, n_layers=layers, max_tokens=T) as eng:
+        lws = []
+        for layer in range(layers):
+            lw = synth.make_layer(shape, seed=layer)
+            eng.load_layer(layer, lw)
+            lws.append(lw)
+        t = torch.from_numpy(x_bits.view(np.int16)).cuda().view(torch.bfloat16)
+        for layer in range(layers):
+            out, sc, ti, tw = eng.forward(layer, t, side=True)
+            h_bits = eng.last_intermediate(T)
+            torch.cuda.synchronize()
+            assert eng.device_status() == 0
+            res = {"out": out.cpu().numpy(), "topk_i": ti.cpu().numpy(), "topk_w": tw.cpu().numpy(),
+                   "h_bits": h_bits.cpu().numpy().view(np.uint16)}
+            ref = oracle_case(lws[layer], x_bits)
+            print("config1 layer", layer, compare(res, ref, 4, f"config 1 layer {layer}"))
+            ref["cache"].drop()
+
+
+def test_plain_c_caller(tmp_path):
+    """tests/c_abi_smoke.c -- a C99 program that includes only include/moe_b200.h and
+    links the shipped library, i.e. the engine-side binding as code -- runs a small
+    layer through the host-buffer entry point; its outputs are checked against the
+    oracle on the inputs it used."""
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe, dump = tmp_path / "c_abi_smoke", tmp_path / "out.bin"
+    lib_dir = os.path.dirname(capi.LIB_PATH)
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic",
+                    "-I", os.path.join(root, "include"), os.path.join(root, "tests", "c_abi_smoke.c"),
+                    "-L", lib_dir, "-l:libmoe_b200.so", f"-Wl,-rpath,{lib_dir}", "-o", str(exe)],
+                   check=True, capture_output=True, text=True)
+    run = subprocess.run([str(exe), str(dump)], capture_output=True, text=True)
+    assert run.returncode == 0 and "c_abi_smoke ok" in run.stdout, run.stdout + run.stderr
+    assert "no device" not in run.stdout
+    raw = open(dump, "rb").read()
+    T, H, E, K, I = np.frombuffer(raw, dtype=np.int32, count=5)
+    pos = [20]
+
+    def take(dtype, *shape):
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        a = np.frombuffer(raw, dtype=dtype, count=int(np.prod(shape)), offset=pos[0]).reshape(shape)
+        pos[0] += n
+        return a
+
+    x_bits, w_router = take(np.uint16, T, H), take(np.uint16, E, H)
+    b_router = take(np.float32, E)
+    blocks1, scales1, bias1 = take(np.uint8, E, 2 * I, H // 32, 16), take(np.uint8, E, 2 * I, H // 32), take(np.float32, E, 2 * I)
+    blocks2, scales2, bias2 = take(np.uint8, E, H, I // 32, 16), take(np.uint8, E, H, I // 32), take(np.float32, E, H)
+    res = {"topk_i": take(np.int32, T, K), "topk_w": take(np.float32, T, K), "out": take(np.float32, T, H)}
+    assert pos[0] == len(raw)
+    shape = pkg.MoEShape(hidden=int(H), intermediate=int(I), n_experts=int(E), top_k=int(K))
+    lw = synth.LayerWeights(shape, w_router, b_router, blocks1, scales1, bias1, blocks2, scales2, bias2)
+    ref = oracle_case(lw, x_bits)
+    ref.pop("h")
+    print("plain C caller", compare(res, ref, int(K), "plain C caller"))
 
 
 # --------------------------------------------------------------------------

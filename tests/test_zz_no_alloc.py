@@ -12,8 +12,11 @@ most 2048 tokens and 256 experts per call).
 This test calls it through the C ABI twice in a row on different batches --
 the array keeps the first call's contents, and the second, smaller batch must
 not see them -- and compares expert indices, routing weights and per-expert
-counts with what the handle-based moe_b200_forward reports for the same inputs.
-It is the last test file on purpose, and passes on its own in a fresh process.
+counts with what the handle-based moe_b200_forward reports for the same inputs,
+and with the CPU oracle's router.  A second test interleaves it with handles of
+other hidden sizes: the routing kernel's shared-memory limit is a per-device
+setting that all of them share.  It is the last test file on purpose, and passes
+on its own in a fresh process.
 """
 import ctypes
 
@@ -23,6 +26,8 @@ import torch
 
 import gpt_oss_amd_b200 as pkg
 from gpt_oss_amd_b200 import capi, synth
+from oracle import oracle
+from oracle.parity import tie_mask
 
 pytestmark = pytest.mark.gpu
 
@@ -66,6 +71,46 @@ def test_route_noalloc_matches_forward_on_two_calls_in_a_row():
             assert np.array_equal(cnt, ref_cnt), f"call {call}"
             assert cnt.sum() == T * shape.top_k
             assert np.array_equal(off, np.concatenate([[0], np.cumsum(cnt)])), f"call {call}"
+            # and against the CPU engine's router (double-accumulated logits, ties excluded)
+            scores, o_i, o_w = oracle.route(synth.bf16_bits_to_f32(x_bits),
+                                            synth.bf16_bits_to_f32(lw.w_router), lw.b_router,
+                                            shape.top_k, round_mode=1)
+            ok = ~tie_mask(scores, shape.top_k)
+            assert np.array_equal(ti[ok], o_i[ok]), f"call {call}"
+            assert np.abs(tw[ok] - o_w[ok]).max() < 1e-5, f"call {call}"
+            if ok.all():
+                assert np.array_equal(cnt, np.bincount(o_i.reshape(-1), minlength=shape.n_experts))
+
+
+def test_route_noalloc_interleaved_with_handles_of_other_hidden_sizes():
+    """The shared-memory opt-in of the routing kernel belongs to the device, not to a
+    caller: a handle with a small hidden size used between two allocation-free calls
+    at a large one must not shrink the limit under the second call."""
+    E, K = 32, 4
+    big = pkg.MoEShape(hidden=2880, intermediate=64, n_experts=E, top_k=K)
+    small = pkg.MoEShape(hidden=256, intermediate=64, n_experts=E, top_k=K)
+    lw_big = synth.make_layer(big, seed=41)
+    w_router = torch.from_numpy(lw_big.w_router.view(np.int16)).cuda()
+    b_router = torch.from_numpy(lw_big.b_router).cuda()
+    x_bits = synth.make_tokens(200, big.hidden, seed=41)
+    t = torch.from_numpy(x_bits.view(np.int16)).cuda().view(torch.bfloat16)
+    first = _route_noalloc(t, w_router, b_router, E, K)
+    lw_small = synth.make_layer(small, seed=42)
+    with pkg.MoEEngine(small, max_tokens=64) as eng:
+        eng.load_layer(0, lw_small)
+        ts = torch.from_numpy(synth.make_tokens(50, small.hidden, seed=42).view(np.int16)).cuda()
+        eng.forward(0, ts.view(torch.bfloat16))
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+        second = _route_noalloc(t, w_router, b_router, E, K)
+    for a, b in zip(first, second):
+        assert np.array_equal(a, b)
+    with pkg.MoEEngine(big, max_tokens=256) as eng:
+        eng.load_layer(0, lw_big)
+        _, _, ref_i, ref_w = eng.forward(0, t, side=True)
+        torch.cuda.synchronize()
+        assert np.array_equal(second[0], ref_i.cpu().numpy())
+        assert np.array_equal(second[1], ref_w.cpu().numpy())
 
 
 def test_route_noalloc_rejects_sizes_beyond_its_fixed_scratch():
