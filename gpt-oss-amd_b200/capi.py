@@ -21,7 +21,7 @@ EP_PEER_EXPORT_BYTES = 256
 #: every symbol include/moe_b200.h declares
 SYMBOLS = [
     "moe_b200_shard_range", "moe_b200_create", "moe_b200_destroy", "moe_b200_set_router",
-    "moe_b200_set_experts_mxfp4", "moe_b200_forward", "moe_b200_forward_host",
+    "moe_b200_set_experts_mxfp4", "moe_b200_forward", "moe_b200_forward_norm", "moe_b200_forward_host",
     "moe_b200_ep_unique_id", "moe_b200_ep_init", "moe_b200_ep_plan", "moe_b200_device_bytes",
     "moe_b200_last_error", "moe_b200_device_status", "moe_b200_last_launch_count",
     "moe_b200_last_expert_counts", "moe_b200_mxfp4_unpack", "moe_b200_unpack_resident",
@@ -65,6 +65,7 @@ def _bind(L: ctypes.CDLL) -> ctypes.CDLL:
     L.moe_b200_set_router.argtypes = [vp, ci, vp, vp]
     L.moe_b200_set_experts_mxfp4.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp, vp, vp]
     L.moe_b200_forward.argtypes = [vp, ci, vp, ci, ci, vp, ci, vp, vp, vp, vp]
+    L.moe_b200_forward_norm.argtypes = [vp, ci, vp, vp, ci, ci, vp, ci, vp, vp, vp, vp]
     L.moe_b200_forward_host.argtypes = [vp, ci, vp, ci, ci, vp, vp, vp]
     L.moe_b200_ep_unique_id.argtypes = [ctypes.c_char_p]
     L.moe_b200_ep_init.argtypes = [vp, ctypes.c_char_p]

@@ -63,6 +63,7 @@ struct moe_b200_handle_s {
     int* slot_of = nullptr;     // [T*K] row of each assignment in send order
     int* row_token = nullptr;   // [T*K]
     uint16_t* xs = nullptr;     // [T*K, H] bf16 rows sorted by expert (send order)
+    uint16_t* xn = nullptr;     // [T, H] bf16 block input when the norm in front of it is fused
     uint16_t* hbuf = nullptr;   // [rows_cap, I] bf16
     float* ybuf = nullptr;      // [rows_cap, H] fp32
     int* status = nullptr;
@@ -175,80 +176,95 @@ moe_b200_status check_layer(moe_b200_handle h, int layer) {
     return MOE_B200_OK;
 }
 
-// Batches up to this many tokens are routed by the warp-per-token kernel (RBS
-// tokens per block) so that a decode-sized batch still spreads over the GPU.  Its
-// time grows with the batch (35 us at 256 tokens, 138 us at 2048) while the
-// tensor-core kernel takes ~85 us for anything up to 64 tokens x 148 blocks: the
-// crossover is a little above 1024 tokens.
-constexpr int ROUTE_SMALL_MAX_TOKENS = 1024;
-
 constexpr int TC5_BN = 256;                   // token rows per tile of the large-batch GEMM
 constexpr int SWAP_MAX_ROWS_PER_EXPERT = 96;  // at most this many rows per expert: small-batch GEMM
 
-// Largest hidden size the warp-per-token router stages in shared memory.
-constexpr size_t ROUTE_SMALL_SMEM_LIMIT = 200 * 1024;
-
-int route_block_tokens(int T, int H) {
-    return (T <= ROUTE_SMALL_MAX_TOKENS && route_small_smem_bytes(H) <= ROUTE_SMALL_SMEM_LIMIT) ? RBS : RB;
+// Token rows per routing block (16 x the router kernel's MT): a block streams the whole
+// router matrix from L2 whatever its height, so large batches use tall blocks and small
+// ones short blocks that still spread over the SMs.  `nt` = ceil(E / 32).
+int route_block_tokens(int T, int nt) {
+    if (T <= 4736)
+        return 16;
+    if (T <= 9472 || nt > 4)  // 8 expert tiles: at most 32 rows per block (registers)
+        return 32;
+    return 64;
 }
 
-// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to (device, kernel), not to
-// a handle: every user of route_small_kernel<NT> -- any handle's forward and the
-// handle-free moe_b200_route_noalloc -- raises it through this one function, once
-// per device and instantiation, to the largest size any of them can ask for, so
-// that no later caller can lower the limit under an earlier one.
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to (device, kernel), not to a
+// handle.  The router kernel's shared memory depends only on its template
+// parameters, so every caller -- any handle's forward and the handle-free
+// moe_b200_route_noalloc -- asks for the same value; it is set once per device and
+// instantiation through this one function and never lowered.
 constexpr int MAX_DEVICES = 64;
-int g_route_small_attr[MAX_DEVICES];  // bit per NT instantiation
+int g_route_attr[MAX_DEVICES];  // bit per (NT, MT) instantiation
 
-template <int NT>
-cudaError_t ensure_route_small_attr(int dev) {
-    const int bit = NT == 1 ? 1 : NT == 2 ? 2 : NT == 4 ? 4 : 8;
+template <int NT, int MT>
+cudaError_t ensure_route_attr(int dev) {
+    constexpr int bit = 1 << ((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (MT == 1 ? 0 : MT == 2 ? 1 : 2));
     if (dev < 0 || dev >= MAX_DEVICES)
         return cudaErrorInvalidDevice;
-    if (g_route_small_attr[dev] & bit)
+    if (g_route_attr[dev] & bit)
         return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(route_small_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)ROUTE_SMALL_SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(route_tc_kernel<NT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)route_tc_smem_bytes<NT, MT>());
     if (e == cudaSuccess)
-        g_route_small_attr[dev] |= bit;
+        g_route_attr[dev] |= bit;
     return e;
 }
 
-template <int NT>
-moe_b200_status launch_route(moe_b200_handle h, const void* t, int t_dtype, int T,
-                             const LayerWeights& lw, float* score_out, int nblk, cudaStream_t st) {
-    if (route_block_tokens(T, h->cfg.hidden_dim) == RBS) {
-        const size_t smem = route_small_smem_bytes(h->cfg.hidden_dim);
-        CU_TRY(h, ensure_route_small_attr<NT>(h->cfg.device));
-        route_small_kernel<NT><<<nblk, RBS * 32, smem, st>>>(
-            t, t_dtype == MOE_B200_DTYPE_F32, T, h->cfg.hidden_dim, lw.w_router, lw.b_router,
-            h->cfg.n_experts, h->cfg.experts_per_token, score_out, h->topk_i, h->topk_w, h->blk_hist);
-        // a launch that failed must not be followed by kernels that consume its output
-        CU_TRY(h, cudaGetLastError());
-        return MOE_B200_OK;
+struct RouteArgs {
+    const void* x;
+    int x_is_f32, T, H;
+    const uint16_t* w_router;
+    const float* b_router;
+    int E, K;
+    const void* rms_w;
+    int rms_w_is_f32;
+    uint16_t* xn_out;
+    float* score_out;
+    int* topk_i;
+    float* topk_w;
+    int* blk_hist;
+};
+
+template <int NT, int MT>
+cudaError_t launch_route_tc(int dev, const RouteArgs& a, cudaStream_t st) {
+    cudaError_t e = ensure_route_attr<NT, MT>(dev);
+    if (e != cudaSuccess)
+        return e;
+    const int nblk = ceil_div(a.T, 16 * MT);
+    route_tc_kernel<NT, MT><<<nblk, RTHREADS, route_tc_smem_bytes<NT, MT>(), st>>>(
+        a.x, a.x_is_f32, a.T, a.H, a.w_router, a.b_router, a.E, a.K, a.rms_w, a.rms_w_is_f32, a.xn_out,
+        a.score_out, a.topk_i, a.topk_w, a.blk_hist);
+    // a launch that failed must not be followed by kernels that consume its output
+    return cudaGetLastError();
+}
+
+// rb = rows per routing block as route_block_tokens() chose them.
+cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
+    const int nt = ceil_div(a.E, 32);
+#define ROUTE_CASE(NT_)                                  \
+    do {                                                 \
+        if (rb == 16)                                    \
+            return launch_route_tc<NT_, 1>(dev, a, st);  \
+        if (rb == 32)                                    \
+            return launch_route_tc<NT_, 2>(dev, a, st);  \
+    } while (0)
+    if (nt <= 1) {
+        ROUTE_CASE(1);
+        return launch_route_tc<1, 4>(dev, a, st);
     }
-    if constexpr (NT <= 4) {
-        // up to 128 experts: the tensor-core router (static shared memory)
-        route_mma_kernel<NT><<<nblk, RTHREADS, 0, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T,
-                                                        h->cfg.hidden_dim, lw.w_router, lw.b_router,
-                                                        h->cfg.n_experts, h->cfg.experts_per_token,
-                                                        score_out, h->topk_i, h->topk_w, h->blk_hist);
-        CU_TRY(h, cudaGetLastError());
-        return MOE_B200_OK;
+    if (nt <= 2) {
+        ROUTE_CASE(2);
+        return launch_route_tc<2, 4>(dev, a, st);
     }
-    const size_t smem = route_smem_bytes<NT>();
-    if (!(h->smem_attr_done & 16) && smem > 48 * 1024) {
-        // the size depends on NT only: every handle sets the same value
-        CU_TRY(h, cudaFuncSetAttribute(route_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem));
+    if (nt <= 4) {
+        ROUTE_CASE(4);
+        return launch_route_tc<4, 4>(dev, a, st);
     }
-    h->smem_attr_done |= 16;
-    route_kernel<NT><<<nblk, RTHREADS, smem, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T,
-                                                   h->cfg.hidden_dim, lw.w_router, lw.b_router,
-                                                   h->cfg.n_experts, h->cfg.experts_per_token,
-                                                   score_out, h->topk_i, h->topk_w, h->blk_hist);
-    CU_TRY(h, cudaGetLastError());
-    return MOE_B200_OK;
+    ROUTE_CASE(8);
+#undef ROUTE_CASE
+    return cudaErrorInvalidValue;
 }
 
 // Large batches on CTA pairs (gemm_tc5_pair.cuh): cluster launch, one cluster per SM pair.
@@ -504,9 +520,12 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
     h->stride2 = (size_t)h->m_tiles2 * h->ks2 * CHUNK_BYTES;
     h->rows_cap = c.max_tokens * K * c.ep_size;
     {
-        const int small = c.max_tokens < ROUTE_SMALL_MAX_TOKENS ? c.max_tokens : ROUTE_SMALL_MAX_TOKENS;
-        const int a = ceil_div(c.max_tokens, RB), b = ceil_div(small, RBS);
-        h->nblk_cap = a > b ? a : b;
+        // most routing blocks any batch up to max_tokens can have
+        const int nt = ceil_div(E, 32);
+        const int steps[3] = {std::min(c.max_tokens, 4736), std::min(c.max_tokens, 9472), c.max_tokens};
+        h->nblk_cap = 1;
+        for (int i = 0; i < 3; i++)
+            h->nblk_cap = std::max(h->nblk_cap, ceil_div(steps[i], route_block_tokens(steps[i], nt)));
     }
 
     moe_b200_status st = MOE_B200_OK;
@@ -536,6 +555,7 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         (st = dev_alloc(h, &h->cnt, E)) || (st = dev_alloc(h, &h->off, E + 1)) ||
         (st = dev_alloc(h, &h->tile_start, E + 1)) || (st = dev_alloc(h, &h->slot_of, TK)) ||
         (st = dev_alloc(h, &h->row_token, TK)) || (st = dev_alloc(h, &h->xs, TK * H)) ||
+        (st = dev_alloc(h, &h->xn, (size_t)c.max_tokens * H)) ||
         (st = dev_alloc(h, &h->hbuf, (size_t)h->rows_cap * I)) ||
         (st = dev_alloc(h, &h->status, 2)) ||
         (st = dev_alloc(h, (float**)&h->t_dev, (size_t)c.max_tokens * H)) ||
@@ -679,9 +699,17 @@ moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int fir
     return MOE_B200_OK;
 }
 
-moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, int t_dtype,
-                                 int n_tokens, float* out, int accumulate, float* router_score_out,
-                                 int* topk_i_out, float* topk_w_out, moe_b200_stream stream) {
+}  // extern "C"
+
+namespace {
+
+// The block.  With `rms_w` the input is the fp32 residual stream: the router kernel
+// applies the norm, writes the normalised rows as bf16 into the handle's workspace
+// and the permute kernel gathers from there.
+moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_dtype, const void* rms_w,
+                             int rms_w_dtype, int n_tokens, float* out, int accumulate,
+                             float* router_score_out, int* topk_i_out, float* topk_w_out,
+                             moe_b200_stream stream) {
     moe_b200_status st = check_layer(h, layer);
     if (st)
         return st;
@@ -690,6 +718,10 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
         return fail(h, MOE_B200_ERR_INVALID, "n_tokens outside [0, max_tokens]");
     if (t_dtype != MOE_B200_DTYPE_F32 && t_dtype != MOE_B200_DTYPE_BF16)
         return fail(h, MOE_B200_ERR_INVALID, "unknown activation dtype");
+    if (rms_w && (rms_w_dtype != MOE_B200_DTYPE_F32 && rms_w_dtype != MOE_B200_DTYPE_BF16))
+        return fail(h, MOE_B200_ERR_INVALID, "unknown norm weight dtype");
+    if (rms_w && t_dtype != MOE_B200_DTYPE_F32)
+        return fail(h, MOE_B200_ERR_INVALID, "the fused norm takes the fp32 residual stream");
     if (n_tokens > 0 && (!t || !out))
         return fail(h, MOE_B200_ERR_INVALID, "null activation / output pointer");
     LayerWeights& lw = h->layers[layer];
@@ -705,7 +737,7 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     CU_TRY(h, cudaSetDevice(c.device));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int T = n_tokens, H = c.hidden_dim, E = c.n_experts, K = c.experts_per_token;
-    const int rb = route_block_tokens(T, H);
+    const int rb = route_block_tokens(T, ceil_div(E, 32));
     const int nblk = ceil_div(T, rb);
     const int bn_local = pick_bn(h, T * K);  // ep_size == 1: the GEMMs run on this rank's own rows
     h->last_launches = 0;
@@ -714,19 +746,16 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
 
     if (T > 0) {
         prof_mark(h, MOE_B200_STAGE_ROUTE, true, s);
-        const int nt = ceil_div(E, 32);
-        if (nt <= 1)
-            st = launch_route<1>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
-        else if (nt <= 2)
-            st = launch_route<2>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
-        else if (nt <= 4)
-            st = launch_route<4>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
-        else
-            st = launch_route<8>(h, t, t_dtype, T, lw, router_score_out, nblk, s);
-        if (st)
-            return st;
+        RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, T, H, lw.w_router, lw.b_router, E, K, rms_w,
+                     rms_w_dtype == MOE_B200_DTYPE_F32, h->xn, router_score_out, h->topk_i, h->topk_w,
+                     h->blk_hist};
+        CU_TRY(h, launch_route(c.device, ra, rb, s));
         prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
         h->last_launches++;
+        if (rms_w) {  // the later kernels read the normalised bf16 rows
+            t = h->xn;
+            t_dtype = MOE_B200_DTYPE_BF16;
+        }
     }
     // plan + permute also run for T == 0 on an expert-parallel rank (nblk == 0
     // gives all-zero counts), so that the exchange below always has its inputs
@@ -826,6 +855,27 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
     }
     CU_TRY(h, cudaGetLastError());
     return MOE_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, int t_dtype,
+                                 int n_tokens, float* out, int accumulate, float* router_score_out,
+                                 int* topk_i_out, float* topk_w_out, moe_b200_stream stream) {
+    return forward_impl(h, layer, t, t_dtype, nullptr, 0, n_tokens, out, accumulate, router_score_out,
+                        topk_i_out, topk_w_out, stream);
+}
+
+moe_b200_status moe_b200_forward_norm(moe_b200_handle h, int layer, const float* x, const void* rms_weight,
+                                      int rms_weight_dtype, int n_tokens, float* out, int accumulate,
+                                      float* router_score_out, int* topk_i_out, float* topk_w_out,
+                                      moe_b200_stream stream) {
+    if (!rms_weight)
+        return fail(h, MOE_B200_ERR_INVALID, "null norm weight");
+    return forward_impl(h, layer, x, MOE_B200_DTYPE_F32, rms_weight, rms_weight_dtype, n_tokens, out,
+                        accumulate, router_score_out, topk_i_out, topk_w_out, stream);
 }
 
 moe_b200_status moe_b200_forward_host(moe_b200_handle h, int layer, const void* t_host, int t_dtype,
@@ -1100,7 +1150,7 @@ moe_b200_status moe_b200_last_intermediate(moe_b200_handle h, int n_tokens, uint
 
 namespace {
 
-constexpr int NA_MAX_BLOCKS = MOE_B200_ROUTE_NOALLOC_MAX_TOKENS / RBS;  // routing blocks of RBS tokens
+constexpr int NA_MAX_BLOCKS = MOE_B200_ROUTE_NOALLOC_MAX_TOKENS / 16;  // routing blocks of 16 tokens
 constexpr int NA_HIST_INTS = NA_MAX_BLOCKS * MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS;
 constexpr int NA_SCRATCH_INTS = 2 * NA_HIST_INTS + MOE_B200_ROUTE_NOALLOC_MAX_EXPERTS + 1;
 constexpr int NA_MAX_DEVICES = MAX_DEVICES;
@@ -1108,33 +1158,12 @@ constexpr int NA_MAX_DEVICES = MAX_DEVICES;
 // [0, NA_HIST_INTS)              per-block expert histograms (router kernel -> plan kernel)
 // [NA_HIST_INTS, 2*NA_HIST_INTS) per-block row bases (written by the plan kernel, unused here)
 // [2*NA_HIST_INTS, ...)          tile table of the plan kernel (unused here)
-// About 0.5 MB per GPU.  In host code this name is only a stand-in for the
+// About 0.26 MB per GPU.  In host code this name is only a stand-in for the
 // symbol, not a device address: kernels get the pointer cudaGetSymbolAddress
 // returns for the current device.
 static __device__ __align__(256) int g_route_noalloc_scratch[NA_SCRATCH_INTS];
 
 int* g_na_scratch_ptr[NA_MAX_DEVICES];  // per device, filled by the first call there
-
-template <int NT>
-moe_b200_status route_noalloc_launch(int dev, const void* t, int t_dtype, int T, int H,
-                                     const uint16_t* w, const float* b, int E, int K, int* topk_i,
-                                     float* topk_w, int* counts, int* offsets, cudaStream_t st) {
-    const size_t smem = route_small_smem_bytes(H);
-    static_assert((size_t)(RBS + RGE) * MOE_B200_ROUTE_NOALLOC_MAX_HIDDEN * 2 + 256 * sizeof(int) <=
-                      ROUTE_SMALL_SMEM_LIMIT,
-                  "the largest hidden size of the allocation-free entry point must fit the shared limit");
-    CU_TRY(nullptr, ensure_route_small_attr<NT>(dev));
-    int* scratch = g_na_scratch_ptr[dev];
-    int* blk_hist = scratch;
-    int* blk_base = scratch + NA_HIST_INTS;
-    int* tile_start = scratch + 2 * NA_HIST_INTS;
-    const int nblk = ceil_div(T, RBS);
-    route_small_kernel<NT><<<nblk, RBS * 32, smem, st>>>(t, t_dtype == MOE_B200_DTYPE_F32, T, H, w, b, E,
-                                                        K, nullptr, topk_i, topk_w, blk_hist);
-    plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, E, 1, counts, offsets, tile_start, blk_base);
-    CU_TRY(nullptr, cudaGetLastError());
-    return MOE_B200_OK;
-}
 
 }  // namespace
 
@@ -1184,23 +1213,20 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
         g_na_scratch_ptr[dev] = p;
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const uint16_t* w = static_cast<const uint16_t*>(w_router_bf16);
-    const int nt = ceil_div(n_experts, 32);
-    if (nt <= 1)
-        return route_noalloc_launch<1>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
-                                       experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
-                                       expert_offsets_out, st);
-    if (nt <= 2)
-        return route_noalloc_launch<2>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
-                                       experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
-                                       expert_offsets_out, st);
-    if (nt <= 4)
-        return route_noalloc_launch<4>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
-                                       experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
-                                       expert_offsets_out, st);
-    return route_noalloc_launch<8>(dev, t, t_dtype, n_tokens, hidden_dim, w, b_router, n_experts,
-                                   experts_per_token, topk_i_out, topk_w_out, expert_counts_out,
-                                   expert_offsets_out, st);
+    int* scratch = g_na_scratch_ptr[dev];
+    int* blk_hist = scratch;
+    int* blk_base = scratch + NA_HIST_INTS;
+    int* tile_start = scratch + 2 * NA_HIST_INTS;
+    const int rb = 16;  // NA_MAX_BLOCKS is sized for it
+    const int nblk = ceil_div(n_tokens, rb);
+    RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, n_tokens, hidden_dim,
+                 static_cast<const uint16_t*>(w_router_bf16), b_router, n_experts, experts_per_token,
+                 nullptr, 0, nullptr, nullptr, topk_i_out, topk_w_out, blk_hist};
+    CU_TRY(nullptr, launch_route(dev, ra, rb, st));
+    plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, n_experts, 1, expert_counts_out, expert_offsets_out,
+                                   tile_start, blk_base);
+    CU_TRY(nullptr, cudaGetLastError());
+    return MOE_B200_OK;
 }
 
 moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local_expert, int which,

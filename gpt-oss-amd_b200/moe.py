@@ -115,6 +115,31 @@ class MoEEngine:
             _ptr(ti), _ptr(tw), ctypes.c_void_p(s.cuda_stream)), self._h, self._lib)
         return (out, sc, ti, tw) if side else out
 
+    def forward_norm(self, layer: int, x: torch.Tensor, rms_weight: torch.Tensor,
+                     out: torch.Tensor | None = None, accumulate: bool = False, side: bool = False,
+                     stream=None):
+        """The block with the RMSNorm in front of it fused in.  x: CUDA fp32 [T, H], the
+        residual stream; rms_weight: CUDA [H] fp32 or bf16.  ``out`` may be ``x`` itself
+        (with ``accumulate=True``: x += MoE(rmsnorm(x)), the engine's residual update)."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] == self.shape.hidden
+        assert rms_weight.is_cuda and rms_weight.numel() == self.shape.hidden
+        assert rms_weight.dtype in (torch.bfloat16, torch.float32)
+        T = x.shape[0]
+        wdt = capi.DTYPE_BF16 if rms_weight.dtype == torch.bfloat16 else capi.DTYPE_F32
+        if out is None:
+            assert not accumulate
+            out = torch.empty(T, self.shape.hidden, dtype=torch.float32, device=x.device)
+        sc = ti = tw = None
+        if side:
+            sc = torch.empty(T, self.shape.n_experts, dtype=torch.float32, device=x.device)
+            ti = torch.empty(T, self.shape.top_k, dtype=torch.int32, device=x.device)
+            tw = torch.empty(T, self.shape.top_k, dtype=torch.float32, device=x.device)
+        s = stream if stream is not None else torch.cuda.current_stream(x.device)
+        capi.check(self._lib.moe_b200_forward_norm(
+            self._h, layer, _ptr(x.contiguous()), _ptr(rms_weight.contiguous()), wdt, T, _ptr(out),
+            int(accumulate), _ptr(sc), _ptr(ti), _ptr(tw), ctypes.c_void_p(s.cuda_stream)), self._h, self._lib)
+        return (out, sc, ti, tw) if side else out
+
     def forward_host(self, layer: int, t_host, out_host, topk_i_host=None, topk_w_host=None):
         """Host buffers in and out (torch CPU tensors, ideally pinned, or numpy)."""
         T = t_host.shape[0]

@@ -135,6 +135,22 @@ moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, in
                                  float* router_score_out, int* topk_i_out, float* topk_w_out,
                                  moe_b200_stream stream);
 
+/* The same block with the RMSNorm in front of it fused in (src/forward.cpp:315 +
+ * 317-514: rmsnorm(s->t, x, rms_ffn_w) followed by the MoE block, and with
+ * accumulate != 0 and out == x the residual add behind it, src/forward.cpp:514).
+ *   x            device f32 [n_tokens, H]: the residual stream, NOT normalised
+ *   rms_weight   device [H], f32 (the CPU engine's weights) or bf16 (the GPU
+ *                engine's, include/model.hpp:92) by rms_weight_dtype
+ * The norm follows the CPU engine's arithmetic exactly (src/run.cpp:306-319:
+ * float squares summed in double, eps 1e-5, 1.0f / sqrtf, weight * (scale * x) in
+ * double rounded to float); the result is rounded to bf16 as the block input
+ * always is (src/hip/BLAS.hip:32-40).  out may alias x (every read of x happens in
+ * the first kernel of the call).  Other arguments as moe_b200_forward. */
+moe_b200_status moe_b200_forward_norm(moe_b200_handle h, int layer, const float* x,
+                                      const void* rms_weight, int rms_weight_dtype, int n_tokens,
+                                      float* out, int accumulate, float* router_score_out,
+                                      int* topk_i_out, float* topk_w_out, moe_b200_stream stream);
+
 /* Same call with HOST buffers: t (pinned or pageable) is copied to the device,
  * the block runs, out is copied back, and the call returns when out is valid.
  * This is the path an engine without device-resident activations would use and

@@ -368,6 +368,28 @@ void oracle_route(int T, int H, int E, int K, int round_mode, const float* t_in,
     free(router_score);
 }
 
+/* The RMSNorm in front of the block (src/run.cpp:306-319; call src/run.cpp:626,
+ * GPU engine src/forward.cpp:315): squares rounded to float and summed in double,
+ * 1.0f / sqrtf of the mean plus 1e-5f in float, then weight * (ss * x) evaluated in
+ * double and stored as float.  rows x size. */
+void oracle_rmsnorm(float* o, const float* x, const float* weight, int rows, int size) {
+    int r, j;
+    for (r = 0; r < rows; r++) {
+        const float* xr = x + (size_t)r * size;
+        float* orow = o + (size_t)r * size;
+        double ss = 0.0f;
+        for (j = 0; j < size; j++) {
+            ss += xr[j] * xr[j];
+        }
+        ss /= size;
+        ss += 1e-5f;
+        ss = 1.0f / sqrtf(ss);
+        for (j = 0; j < size; j++) {
+            orow[j] = weight[j] * (ss * xr[j]);
+        }
+    }
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -196,6 +196,19 @@ class ExpertCache:
         self._b.clear()
 
 
+def rmsnorm(x_f32, weight_f32, impl="port"):
+    """The RMSNorm in front of the block (src/run.cpp:306-319), row by row -> [T, H]."""
+    x = np.ascontiguousarray(x_f32, dtype=np.float32)
+    w = np.ascontiguousarray(weight_f32, dtype=np.float32)
+    T, H = x.shape
+    o = np.empty_like(x)
+    if impl == "reference":
+        _lib_ref().ref_rmsnorm(_p(o, _f32p), _p(x, _f32p), _p(w, _f32p), T, H)
+    else:
+        _lib_port().oracle_rmsnorm(_p(o, _f32p), _p(x, _f32p), _p(w, _f32p), T, H)
+    return o
+
+
 def route(x_f32, w_router_f32, b_router, top_k, round_mode=1):
     """Router + top-k + softmax (src/run.cpp:630-641) -> (scores, topk_i, topk_v)."""
     x = np.ascontiguousarray(x_f32, dtype=np.float32)

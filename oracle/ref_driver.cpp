@@ -23,6 +23,11 @@ extern "C" {
 void ref_matmul(float* xout, float* x, float* w, int n, int d) { matmul(xout, x, w, n, d); }
 void ref_softmax(float* x, int size) { softmax(x, size); }
 void ref_topk(float* v, int* i, float* score, int E, int K) { topk(v, i, score, E, K); }
+// The reference's own rmsnorm (src/run.cpp:306-319), row by row.
+void ref_rmsnorm(float* o, float* x, float* weight, int rows, int size) {
+    for (int r = 0; r < rows; r++)
+        rmsnorm(o + (size_t)r * size, x + (size_t)r * size, weight, size);
+}
 int ref_num_threads(void) { return omp_get_max_threads(); }
 // Threads of the calling thread's later parallel regions, whatever OMP_NUM_THREADS
 // the process inherited.

@@ -277,6 +277,45 @@ def test_config1_decode_batch_three_layers():
             ref["cache"].drop()
 
 
+@pytest.mark.parametrize("w_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("H,I,E,T", [(256, 128, 32, 300), (2880, 64, 128, 1500), (2880, 2880, 32, 96)])
+def test_fused_rmsnorm_in_front_of_the_block(H, I, E, T, w_dtype):
+    """moe_b200_forward_norm: the FFN RMSNorm (src/forward.cpp:315, src/run.cpp:306-319)
+    fused into the router kernel.  The oracle is the reference's rmsnorm followed by the
+    block; the fused norm reproduces the CPU engine's arithmetic, so the expert indices
+    must match like everywhere else.  Also the engine's in-place residual update
+    x += MoE(rmsnorm(x)) with out aliasing x."""
+    shape = pkg.MoEShape(hidden=H, intermediate=I, n_experts=E, top_k=4)
+    lw = synth.make_layer(shape, seed=H + T)
+    g = torch.Generator().manual_seed(T)
+    x = (torch.randn(T, H, generator=g) * (0.5 + 4.0 * torch.rand(T, 1, generator=g))).float()
+    w = (1.0 + 0.2 * torch.randn(H, generator=g)).float()
+    w_dev = w.cuda().to(torch.bfloat16) if w_dtype == "bf16" else w.cuda()
+    w_ref = w_dev.float().cpu().numpy()
+    impl = "reference" if oracle.have_reference() else "port"
+    xn = oracle.rmsnorm(x.numpy(), w_ref, impl=impl)
+    x_bits = synth.bf16_bits(torch.from_numpy(xn))
+    ref = oracle_case(lw, x_bits)
+    with pkg.MoEEngine(shape, max_tokens=T) as eng:
+        eng.load_layer(0, lw)
+        out, sc, ti, tw = eng.forward_norm(0, x.cuda(), w_dev, side=True)
+        h_bits = eng.last_intermediate(T)
+        torch.cuda.synchronize()
+        res = {"out": out.cpu().numpy(), "topk_i": ti.cpu().numpy(), "topk_w": tw.cpu().numpy(),
+               "h_bits": h_bits.cpu().numpy().view(np.uint16)}
+        print("fused norm", (H, I, E, T, w_dtype), compare(res, ref, 4, "fused norm"))
+        assert np.abs(sc.cpu().numpy() - ref["router_score"]).max() < 1e-5
+        # the same rows through the separate path: normalised bf16 rows in, identical bits out
+        t = torch.from_numpy(x_bits.view(np.int16)).cuda().view(torch.bfloat16)
+        assert torch.equal(eng.forward(0, t), out)
+        # in place: x += MoE(rmsnorm(x))
+        xr = x.cuda().clone()
+        eng.forward_norm(0, xr, w_dev, out=xr, accumulate=True)
+        torch.cuda.synchronize()
+        assert torch.equal(xr, x.cuda() + out)
+        assert eng.device_status() == 0
+
+
 def test_plain_c_caller(tmp_path):
     """tests/c_abi_smoke.c -- a C99 program that includes only include/moe_b200.h and
     links the shipped library, i.e. the engine-side binding as code -- runs a small

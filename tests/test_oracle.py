@@ -100,3 +100,19 @@ def test_swiglu_clamps_and_gate_has_no_lower_clamp():
     sig = 1.0 / (1.0 + np.exp(np.float32(-1.702 * 7.0)))
     assert np.isclose(y[0, 0], 7.0 * sig * 8.0, rtol=1e-6)
     assert y[0, 1] == 0.0 or abs(y[0, 1]) < 1e-30  # -100 * sigmoid(-170.2) * (-6) ~ 0
+
+
+def test_rmsnorm_port_equals_reference_function():
+    """oracle_rmsnorm against the reference's compiled rmsnorm (src/run.cpp:306-319),
+    bit for bit, and against the formula in numpy."""
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((7, 2880)) * rng.uniform(0.1, 30, size=(7, 1))).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(2880)).astype(np.float32)
+    mine = oracle.rmsnorm(x, w)
+    ss = (x.astype(np.float32) ** 2).astype(np.float64).sum(axis=1) / 2880 + np.float64(np.float32(1e-5))
+    scale = (np.float32(1.0) / np.sqrt(ss.astype(np.float32))).astype(np.float64)
+    want = (w.astype(np.float64) * (scale[:, None] * x.astype(np.float64))).astype(np.float32)
+    assert np.abs(mine - want).max() <= 1e-6 * np.abs(want).max()
+    if oracle.have_reference():
+        ref = oracle.rmsnorm(x, w, impl="reference")
+        assert np.array_equal(mine.view(np.uint32), ref.view(np.uint32))
