@@ -28,7 +28,7 @@ SYMBOLS = [
     "moe_b200_version", "moe_b200_profile", "moe_b200_profile_read",
     "moe_b200_last_intermediate", "moe_b200_route_noalloc",
     "moe_b200_ep_peer_export", "moe_b200_ep_peer_enable", "moe_b200_ep_peer_sequence",
-    "moe_b200_ep_peer_resync",
+    "moe_b200_ep_peer_resync", "moe_b200_expert_file_info", "moe_b200_load_experts_file",
 ]
 N_STAGES = 11
 STAGE_NAMES = ["route", "plan", "permute", "dispatch", "regroup", "gemm1", "gemm2", "return",
@@ -87,6 +87,10 @@ def _bind(L: ctypes.CDLL) -> ctypes.CDLL:
     L.moe_b200_ep_peer_enable.argtypes = [vp, ctypes.c_char_p]
     L.moe_b200_ep_peer_sequence.argtypes = [vp]
     L.moe_b200_ep_peer_resync.argtypes = [vp, ci]
+    fp = ctypes.POINTER(ctypes.c_float)
+    L.moe_b200_expert_file_info.argtypes = [ctypes.c_char_p, ip, ip, ip, ip, ip, fp,
+                                            ctypes.POINTER(ctypes.c_ulonglong)]
+    L.moe_b200_load_experts_file.argtypes = [vp, ctypes.c_char_p, ci, ci]
     L.moe_b200_profile.argtypes = [vp, ci]
     L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
     return L

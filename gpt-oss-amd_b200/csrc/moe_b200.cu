@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -12,11 +13,13 @@
 
 #include "common.cuh"
 #include "ep.cuh"
+#include "expert_file.hpp"
 #ifdef MOE_B200_TEST_AIDS
 #include "gemm_mma.cuh"
 #endif
 #include "gemm_tc5_pair.cuh"
 #include "gemm_tc5_swap.cuh"
+#include "gemm_tc5_ts.cuh"
 #include "mxfp4.cuh"
 #include "plan.cuh"
 #include "route.cuh"
@@ -81,6 +84,7 @@ struct moe_b200_handle_s {
 
     tc5::TensorMaps maps_x{}, maps_h{};  // TMA maps over the GEMM inputs
     int pair_grid = 0;       // CTAs of the pair GEMM (2 x resident clusters)
+    bool small_gemm_ts = true;  // small batches: decoded weights in tensor memory (else in shared memory)
     int smem_attr_done = 0;  // bit set: shared-memory opt-in of a kernel family done on this device
 
     ep::State ep;
@@ -196,71 +200,73 @@ int route_block_tokens(int T, int nt) {
 // moe_b200_route_noalloc -- asks for the same value; it is set once per device and
 // instantiation through this one function and never lowered.
 constexpr int MAX_DEVICES = 64;
-int g_route_attr[MAX_DEVICES];  // bit per (NT, MT) instantiation
-
-template <int NT, int MT>
-cudaError_t ensure_route_attr(int dev) {
-    constexpr int bit = 1 << ((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (MT == 1 ? 0 : MT == 2 ? 1 : 2));
-    if (dev < 0 || dev >= MAX_DEVICES)
-        return cudaErrorInvalidDevice;
-    if (g_route_attr[dev] & bit)
-        return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(route_tc_kernel<NT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)route_tc_smem_bytes<NT, MT>());
-    if (e == cudaSuccess)
-        g_route_attr[dev] |= bit;
-    return e;
-}
+int g_route_attr[MAX_DEVICES];  // bit per (NT, MT, XF32) instantiation
 
 struct RouteArgs {
-    const void* x;
+    const void* x;  // bf16 rows (f32 with x_is_f32: the handle-free entry point only)
     int x_is_f32, T, H;
     const uint16_t* w_router;
     const float* b_router;
     int E, K;
-    const void* rms_w;
-    int rms_w_is_f32;
-    uint16_t* xn_out;
     float* score_out;
     int* topk_i;
     float* topk_w;
     int* blk_hist;
 };
 
-template <int NT, int MT>
+template <int NT, int MT, bool XF32>
 cudaError_t launch_route_tc(int dev, const RouteArgs& a, cudaStream_t st) {
-    cudaError_t e = ensure_route_attr<NT, MT>(dev);
-    if (e != cudaSuccess)
-        return e;
+    constexpr int bit = 1 << (((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (MT == 1 ? 0 : MT == 2 ? 1 : 2)) * 2 +
+                              (XF32 ? 1 : 0));
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return cudaErrorInvalidDevice;
+    if (!(g_route_attr[dev] & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(route_tc_kernel<NT, MT, XF32>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)route_tc_smem_bytes<NT, MT>());
+        if (e != cudaSuccess)
+            return e;
+        g_route_attr[dev] |= bit;
+    }
     const int nblk = ceil_div(a.T, 16 * MT);
-    route_tc_kernel<NT, MT><<<nblk, RTHREADS, route_tc_smem_bytes<NT, MT>(), st>>>(
-        a.x, a.x_is_f32, a.T, a.H, a.w_router, a.b_router, a.E, a.K, a.rms_w, a.rms_w_is_f32, a.xn_out,
-        a.score_out, a.topk_i, a.topk_w, a.blk_hist);
+    route_tc_kernel<NT, MT, XF32><<<nblk, RTHREADS, route_tc_smem_bytes<NT, MT>(), st>>>(
+        a.x, a.T, a.H, a.w_router, a.b_router, a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist);
     // a launch that failed must not be followed by kernels that consume its output
     return cudaGetLastError();
 }
 
-// rb = rows per routing block as route_block_tokens() chose them.
+// rb = rows per routing block as route_block_tokens() chose them (fp32 rows: 16).
 cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
     const int nt = ceil_div(a.E, 32);
-#define ROUTE_CASE(NT_)                                  \
-    do {                                                 \
-        if (rb == 16)                                    \
-            return launch_route_tc<NT_, 1>(dev, a, st);  \
-        if (rb == 32)                                    \
-            return launch_route_tc<NT_, 2>(dev, a, st);  \
+    if (a.x_is_f32) {
+        if (rb != 16)
+            return cudaErrorInvalidValue;
+        if (nt <= 1)
+            return launch_route_tc<1, 1, true>(dev, a, st);
+        if (nt <= 2)
+            return launch_route_tc<2, 1, true>(dev, a, st);
+        if (nt <= 4)
+            return launch_route_tc<4, 1, true>(dev, a, st);
+        return launch_route_tc<8, 1, true>(dev, a, st);
+    }
+#define ROUTE_CASE(NT_)                                         \
+    do {                                                        \
+        if (rb == 16)                                           \
+            return launch_route_tc<NT_, 1, false>(dev, a, st);  \
+        if (rb == 32)                                           \
+            return launch_route_tc<NT_, 2, false>(dev, a, st);  \
     } while (0)
     if (nt <= 1) {
         ROUTE_CASE(1);
-        return launch_route_tc<1, 4>(dev, a, st);
+        return launch_route_tc<1, 4, false>(dev, a, st);
     }
     if (nt <= 2) {
         ROUTE_CASE(2);
-        return launch_route_tc<2, 4>(dev, a, st);
+        return launch_route_tc<2, 4, false>(dev, a, st);
     }
     if (nt <= 4) {
         ROUTE_CASE(4);
-        return launch_route_tc<4, 4>(dev, a, st);
+        return launch_route_tc<4, 4, false>(dev, a, st);
     }
     ROUTE_CASE(8);
 #undef ROUTE_CASE
@@ -369,6 +375,34 @@ moe_b200_status launch_swap(moe_b200_handle h, const LayerWeights& lw, const tc5
     return MOE_B200_OK;
 }
 
+// Small batches, decoded weights in tensor memory (gemm_tc5_ts.cuh).
+moe_b200_status launch_ts(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
+                          const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
+                          const int* row_dst, const peer::GemmPeerIO& pio, cudaStream_t st) {
+    const moe_b200_config& c = h->cfg;
+    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
+    namespace ts = tc5::ts;
+    if (!(h->smem_attr_done & 32)) {
+        CU_TRY(h, cudaFuncSetAttribute(ts::expert_gemm_ts_kernel<0>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, ts::SMEM_BYTES));
+        CU_TRY(h, cudaFuncSetAttribute(ts::expert_gemm_ts_kernel<1>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, ts::SMEM_BYTES));
+        h->smem_attr_done |= 32;
+    }
+    prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
+    ts::expert_gemm_ts_kernel<0><<<h->n_sms, ts::N_THREADS, ts::SMEM_BYTES, st>>>(
+        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
+        EL, h->hbuf, I, I, nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
+    prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
+    ts::expert_gemm_ts_kernel<1><<<h->n_sms, ts::N_THREADS, ts::SMEM_BYTES, st>>>(
+        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
+        EL, yout, H, H, row_dst, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
+    prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
+    h->last_launches += 2;
+    return MOE_B200_OK;
+}
+
 // The two grouped GEMMs over `g_*` tables describing rows grouped by local
 // expert; `bn` is the number of token rows per tile the tables were built for
 // (pick_bn), which also selects the kernel.
@@ -405,8 +439,12 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
     (void)H;
     (void)I;
     (void)EL;
-    if (bn == tc5::swp::BM)
+    if (bn == tc5::swp::BM) {
+        static_assert(tc5::swp::BM == tc5::ts::BN, "both small-batch kernels use tables of 128-row tiles");
+        if (h->small_gemm_ts)
+            return launch_ts(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
         return launch_swap(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
+    }
     if (bn == TC5_BN)
         return launch_pair(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
     return fail(h, MOE_B200_ERR_INVALID, "tile tables were built for another tile height");
@@ -431,6 +469,71 @@ int pick_bn(moe_b200_handle h, int rows) {
 #endif
     const int per_expert = rows / (h->n_local > 0 ? h->n_local : 1);
     return per_expert <= SWAP_MAX_ROWS_PER_EXPERT ? tc5::swp::BM : TC5_BN;
+}
+
+moe_b200_status check_shard(moe_b200_handle h, int first_expert, int n) {
+    if (n <= 0 || first_expert < h->first_expert || first_expert + n > h->first_expert + h->n_local)
+        return fail(h, MOE_B200_ERR_INVALID,
+                    "experts [" + std::to_string(first_expert) + ", " +
+                        std::to_string(first_expert + n) + ") are not inside this rank's shard [" +
+                        std::to_string(h->first_expert) + ", " +
+                        std::to_string(h->first_expert + h->n_local) + ")");
+    return MOE_B200_OK;
+}
+
+// Upload of packed experts: everything is queued on one stream (copy -> re-tile ->
+// next copy into the same staging buffer are ordered by it) and the host waits once,
+// in upload_finish.  Scale bytes the one-multiply decode cannot represent are
+// reported through a flag word of their own, so that an older wait code in the
+// status word cannot mask them.
+moe_b200_status upload_begin(moe_b200_handle h) {
+    CU_TRY(h, cudaMemsetAsync(h->status + 1, 0, sizeof(int), h->own_stream));
+    return MOE_B200_OK;
+}
+
+moe_b200_status upload_expert(moe_b200_handle h, int layer, int le, const uint8_t* b1, const uint8_t* s1,
+                              const float* c1, const uint8_t* b2, const uint8_t* s2, const float* c2) {
+    LayerWeights& lw = h->layers[layer];
+    const int H = h->cfg.hidden_dim, I = h->cfg.intermediate_dim;
+    const int G1 = H / 32, G2 = I / 32;
+    const size_t nb1 = (size_t)2 * I * G1 * 16, ns1 = (size_t)2 * I * G1;
+    const size_t nb2 = (size_t)H * G2 * 16, ns2 = (size_t)H * G2;
+    cudaStream_t s = h->own_stream;
+    int* bad_scale = h->status + 1;
+    if (!(is_device_pointer(b1) && is_device_pointer(s1))) {
+        CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b1, nb1, cudaMemcpyHostToDevice, s));
+        CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s1, ns1, cudaMemcpyHostToDevice, s));
+        b1 = h->stage_blocks;
+        s1 = h->stage_scales;
+    }
+    mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(b1, s1, 2 * I, G1,
+                                                                     lw.w1 + le * h->stride1, bad_scale);
+    if (!(is_device_pointer(b2) && is_device_pointer(s2))) {
+        CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b2, nb2, cudaMemcpyHostToDevice, s));
+        CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s2, ns2, cudaMemcpyHostToDevice, s));
+        b2 = h->stage_blocks;
+        s2 = h->stage_scales;
+    }
+    mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(b2, s2, H, G2,
+                                                                     lw.w2 + le * h->stride2, bad_scale);
+    CU_TRY(h, cudaMemcpyAsync(lw.bias1 + (size_t)le * 2 * I, c1, (size_t)2 * I * 4, cudaMemcpyDefault, s));
+    CU_TRY(h, cudaMemcpyAsync(lw.bias2 + (size_t)le * H, c2, (size_t)H * 4, cudaMemcpyDefault, s));
+    return MOE_B200_OK;
+}
+
+moe_b200_status upload_finish(moe_b200_handle h, int layer, int first_expert, int n) {
+    LayerWeights& lw = h->layers[layer];
+    CU_TRY(h, cudaGetLastError());
+    int sw = 0;
+    CU_TRY(h, cudaMemcpyAsync(&sw, h->status + 1, sizeof(int), cudaMemcpyDeviceToHost, h->own_stream));
+    CU_TRY(h, cudaStreamSynchronize(h->own_stream));
+    for (int i = 0; i < n; i++)
+        lw.expert_set[first_expert + i - h->first_expert] = (sw == 0);
+    if (sw != 0)
+        return fail(h, MOE_B200_ERR_UNSUPPORTED,
+                    "an e8m0 scale byte above 128 (block scale above 2) was found; the in-kernel "
+                    "decode covers scale bytes 0..128");
+    return MOE_B200_OK;
 }
 
 }  // namespace
@@ -510,6 +613,8 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         return fail(nullptr, MOE_B200_ERR_INVALID, "out of host memory");
     h->cfg = c;
     h->n_sms = prop.multiProcessorCount;
+    if (const char* v = getenv("MOE_B200_SMALL_GEMM"))
+        h->small_gemm_ts = strcmp(v, "swap") != 0;
     moe_b200_shard_range(c.n_experts, c.ep_size, c.ep_rank, &h->first_expert, &h->n_local);
     const int H = c.hidden_dim, I = c.intermediate_dim, E = c.n_experts, K = c.experts_per_token;
     h->m_tiles1 = ceil_div(2 * I, TILE_M);
@@ -639,64 +744,88 @@ moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int fir
         return st;
     if (!blocks1 || !scales1 || !bias1 || !blocks2 || !scales2 || !bias2)
         return fail(h, MOE_B200_ERR_INVALID, "null expert pointer");
-    if (n <= 0 || first_expert < h->first_expert || first_expert + n > h->first_expert + h->n_local)
-        return fail(h, MOE_B200_ERR_INVALID,
-                    "experts [" + std::to_string(first_expert) + ", " +
-                        std::to_string(first_expert + n) + ") are not inside this rank's shard [" +
-                        std::to_string(h->first_expert) + ", " +
-                        std::to_string(h->first_expert + h->n_local) + ")");
+    if ((st = check_shard(h, first_expert, n)))
+        return st;
     CU_TRY(h, cudaSetDevice(h->cfg.device));
-    LayerWeights& lw = h->layers[layer];
     const int H = h->cfg.hidden_dim, I = h->cfg.intermediate_dim;
-    const int G1 = H / 32, G2 = I / 32;
-    const size_t nb1 = (size_t)2 * I * G1 * 16, ns1 = (size_t)2 * I * G1;
-    const size_t nb2 = (size_t)H * G2 * 16, ns2 = (size_t)H * G2;
-    const bool dev1 = is_device_pointer(blocks1) && is_device_pointer(scales1);
-    const bool dev2 = is_device_pointer(blocks2) && is_device_pointer(scales2);
-    // Everything is queued on one stream (copy -> re-tile -> next copy into the same
-    // staging buffer are ordered by it) and the host waits once, at the end.
-    cudaStream_t s = h->own_stream;
-    int* bad_scale = h->status + 1;  // its own word: an older wait code cannot mask it
-    CU_TRY(h, cudaMemsetAsync(bad_scale, 0, sizeof(int), s));
+    const size_t nb1 = (size_t)2 * I * (H / 32) * 16, ns1 = (size_t)2 * I * (H / 32);
+    const size_t nb2 = (size_t)H * (I / 32) * 16, ns2 = (size_t)H * (I / 32);
+    if ((st = upload_begin(h)))
+        return st;
     for (int i = 0; i < n; i++) {
-        const int le = first_expert + i - h->first_expert;
-        const uint8_t *b1 = blocks1 + i * nb1, *s1 = scales1 + i * ns1;
-        const uint8_t *b2 = blocks2 + i * nb2, *s2 = scales2 + i * ns2;
-        if (!dev1) {
-            CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b1, nb1, cudaMemcpyHostToDevice, s));
-            CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s1, ns1, cudaMemcpyHostToDevice, s));
-            b1 = h->stage_blocks;
-            s1 = h->stage_scales;
-        }
-        mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(b1, s1, 2 * I, G1,
-                                                                         lw.w1 + le * h->stride1, bad_scale);
-        if (!dev2) {
-            CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b2, nb2, cudaMemcpyHostToDevice, s));
-            CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s2, ns2, cudaMemcpyHostToDevice, s));
-            b2 = h->stage_blocks;
-            s2 = h->stage_scales;
-        }
-        mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(b2, s2, H, G2,
-                                                                         lw.w2 + le * h->stride2, bad_scale);
-        CU_TRY(h, cudaMemcpyAsync(lw.bias1 + (size_t)le * 2 * I, bias1 + (size_t)i * 2 * I,
-                                  (size_t)2 * I * 4, cudaMemcpyDefault, s));
-        CU_TRY(h, cudaMemcpyAsync(lw.bias2 + (size_t)le * H, bias2 + (size_t)i * H, (size_t)H * 4,
-                                  cudaMemcpyDefault, s));
+        if ((st = upload_expert(h, layer, first_expert + i - h->first_expert, blocks1 + i * nb1,
+                                scales1 + i * ns1, bias1 + (size_t)i * 2 * I, blocks2 + i * nb2,
+                                scales2 + i * ns2, bias2 + (size_t)i * H)))
+            return st;
     }
-    CU_TRY(h, cudaGetLastError());
-    int sw = 0;
-    CU_TRY(h, cudaMemcpyAsync(&sw, bad_scale, sizeof(int), cudaMemcpyDeviceToHost, s));
-    CU_TRY(h, cudaStreamSynchronize(s));
-    if (sw != 0) {
-        for (int i = 0; i < n; i++)
-            lw.expert_set[first_expert + i - h->first_expert] = 0;
-        return fail(h, MOE_B200_ERR_UNSUPPORTED,
-                    "an e8m0 scale byte above 128 (block scale above 2) was found; the in-kernel "
-                    "decode covers scale bytes 0..128");
-    }
-    for (int i = 0; i < n; i++)
-        lw.expert_set[first_expert + i - h->first_expert] = 1;
+    return upload_finish(h, layer, first_expert, n);
+}
+
+moe_b200_status moe_b200_expert_file_info(const char* path, int* n_layers, int* n_experts,
+                                          int* hidden_dim, int* intermediate_dim,
+                                          int* experts_per_token, float* swiglu_limit,
+                                          unsigned long long* file_bytes) {
+    if (!path)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "null path");
+    efile::Mapping m;
+    const std::string err = efile::open_file(path, m);
+    if (!err.empty())
+        return fail(nullptr, MOE_B200_ERR_INVALID, err);
+    const efile::RefConfig& c = m.hdr.config;
+    if (n_layers)
+        *n_layers = c.n_layers;
+    if (n_experts)
+        *n_experts = c.n_experts;
+    if (hidden_dim)
+        *hidden_dim = c.hidden_dim;
+    if (intermediate_dim)
+        *intermediate_dim = c.intermediate_dim;
+    if (experts_per_token)
+        *experts_per_token = c.experts_per_token;
+    if (swiglu_limit)
+        *swiglu_limit = c.swiglu_limit;
+    if (file_bytes)
+        *file_bytes = m.hdr.file_bytes;
     return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_load_experts_file(moe_b200_handle h, const char* path, int file_layer, int layer) {
+    moe_b200_status st = check_layer(h, layer);
+    if (st)
+        return st;
+    if (!path)
+        return fail(h, MOE_B200_ERR_INVALID, "null path");
+    efile::Mapping m;
+    const std::string err = efile::open_file(path, m);
+    if (!err.empty())
+        return fail(h, MOE_B200_ERR_INVALID, err);
+    const efile::RefConfig& fc = m.hdr.config;
+    const moe_b200_config& c = h->cfg;
+    if (fc.hidden_dim != c.hidden_dim || fc.intermediate_dim != c.intermediate_dim ||
+        fc.n_experts != c.n_experts || fc.experts_per_token != c.experts_per_token)
+        return fail(h, MOE_B200_ERR_INVALID,
+                    std::string(path) + ": dimensions differ from the handle's (file: H " +
+                        std::to_string(fc.hidden_dim) + ", I " + std::to_string(fc.intermediate_dim) + ", E " +
+                        std::to_string(fc.n_experts) + ", K " + std::to_string(fc.experts_per_token) + ")");
+    if (file_layer < 0 || file_layer >= fc.n_layers)
+        return fail(h, MOE_B200_ERR_INVALID, "the file has no such layer");
+    CU_TRY(h, cudaSetDevice(c.device));
+    const int H = c.hidden_dim, I = c.intermediate_dim, E = c.n_experts;
+    const unsigned char* r = efile::router_of(m, file_layer);
+    if ((st = moe_b200_set_router(h, layer, r, reinterpret_cast<const float*>(r + (size_t)E * H * 2))))
+        return st;
+    // only the records of this rank's shard are touched (and so paged in)
+    const efile::RecordLayout rl = efile::record_layout(H, I);
+    if ((st = upload_begin(h)))
+        return st;
+    for (int le = 0; le < h->n_local; le++) {
+        const unsigned char* rec = efile::record_of(m, file_layer, h->first_expert + le);
+        if ((st = upload_expert(h, layer, le, rec + rl.blocks1, rec + rl.scales1,
+                                reinterpret_cast<const float*>(rec + rl.bias1), rec + rl.blocks2,
+                                rec + rl.scales2, reinterpret_cast<const float*>(rec + rl.bias2))))
+            return st;
+    }
+    return upload_finish(h, layer, h->first_expert, h->n_local);  // waits for the copies: the mapping can go
 }
 
 }  // extern "C"
@@ -746,16 +875,22 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
 
     if (T > 0) {
         prof_mark(h, MOE_B200_STAGE_ROUTE, true, s);
-        RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, T, H, lw.w_router, lw.b_router, E, K, rms_w,
-                     rms_w_dtype == MOE_B200_DTYPE_F32, h->xn, router_score_out, h->topk_i, h->topk_w,
+        if (t_dtype == MOE_B200_DTYPE_F32) {
+            // fp32 rows (the engine's s->t, or with rms_w its residual stream) become the
+            // bf16 rows every later kernel reads: one pass, norm folded in when asked
+            if (H > 4 * RCAST_THREADS * RCAST_MAX_VEC)
+                return fail(h, MOE_B200_ERR_UNSUPPORTED, "fp32 input is supported up to hidden_dim 8192");
+            rows_to_bf16_kernel<<<T, RCAST_THREADS, 0, s>>>(static_cast<const float*>(t), T, H, rms_w,
+                                                           rms_w_dtype == MOE_B200_DTYPE_F32, h->xn);
+            h->last_launches++;
+            t = h->xn;
+            t_dtype = MOE_B200_DTYPE_BF16;
+        }
+        RouteArgs ra{t, 0, T, H, lw.w_router, lw.b_router, E, K, router_score_out, h->topk_i, h->topk_w,
                      h->blk_hist};
         CU_TRY(h, launch_route(c.device, ra, rb, s));
         prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
         h->last_launches++;
-        if (rms_w) {  // the later kernels read the normalised bf16 rows
-            t = h->xn;
-            t_dtype = MOE_B200_DTYPE_BF16;
-        }
     }
     // plan + permute also run for T == 0 on an expert-parallel rank (nblk == 0
     // gives all-zero counts), so that the exchange below always has its inputs
@@ -1221,7 +1356,7 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
     const int nblk = ceil_div(n_tokens, rb);
     RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, n_tokens, hidden_dim,
                  static_cast<const uint16_t*>(w_router_bf16), b_router, n_experts, experts_per_token,
-                 nullptr, 0, nullptr, nullptr, topk_i_out, topk_w_out, blk_hist};
+                 nullptr, topk_i_out, topk_w_out, blk_hist};
     CU_TRY(nullptr, launch_route(dev, ra, rb, st));
     plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, n_experts, 1, expert_counts_out, expert_offsets_out,
                                    tile_start, blk_base);

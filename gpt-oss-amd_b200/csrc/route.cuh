@@ -1,5 +1,6 @@
-// Router GEMM + bias, top-k, softmax over the selected logits, the per-block
-// expert histogram and (optionally) the RMSNorm in front of the block -- one kernel.
+// Router GEMM + bias, top-k, softmax over the selected logits and the per-block
+// expert histogram -- one kernel; and the fp32 -> bf16 cast of the block input,
+// with the RMSNorm in front of the block folded in when asked.
 //
 // Replaces gemm_router (src/hip/gemms/gemm_router.hip:7-190), topk_kernel
 // (src/hip/topk.hip:5-57), softmax_kernel (src/hip/softmax.hip:5-44), the
@@ -7,14 +8,15 @@
 // when a norm weight is given, rmsnorm (src/hip/rmsnorm.hip:3-37,
 // src/forward.cpp:315; CPU: src/run.cpp:306-319).
 //
-// One kernel family for every batch size: a block owns RB = 16 * MT token rows
-// (MT = 1, 2 or 4, picked by the host so that a small batch still spreads over
-// the GPU) and all experts; warp-level tensor-core MMAs (mma.sync bf16, fp32
-// accumulate) over K chunks of 64 columns.  The router matrix streams through a
-// three-stage cp.async ring (every block reads all of it, from L2), the token
-// rows go through registers one chunk ahead (fp32 input is rounded to bf16 there,
-// and the norm is applied there): one __syncthreads per chunk, loads of chunk
-// c + 2 in flight under the MMAs of chunk c.
+// Router: one kernel family for every batch size.  A block owns RB = 16 * MT
+// token rows (MT = 1, 2 or 4, picked by the host so that a small batch still
+// spreads over the GPU) and all experts; warp-level tensor-core MMAs (mma.sync
+// bf16, fp32 accumulate) over K chunks of 64 columns.  Token rows and router
+// matrix (every block reads all of it, from L2) stream through a deep cp.async
+// ring -- the kernel is a chain of H / 64 dependent chunks per block, so what
+// matters is how many chunks are in flight: as many stages as shared memory holds
+// (up to 12), one __syncthreads per chunk.  Input rows are bf16: fp32 input goes
+// through rows_to_bf16_kernel first.
 //
 // Numerics.  The expert indices must equal those of the CPU engine, which sums
 // float products in a double (src/run.cpp:341-354), for every token whose
@@ -26,12 +28,12 @@
 // (src/run.cpp:635-637).  Measured at H = 2880, E = 128: |logit error| < 2e-6,
 // no index mismatch.  Ties go to the lower expert index (src/hip/topk.hip:30-49).
 //
-// RMSNorm (optional) follows the CPU engine bit for bit: the squares are rounded
-// to float and summed in double, 1.0f / sqrtf((float)(ss / H + 1e-5f)) in IEEE
-// float arithmetic, and o = weight * (scale * x) evaluated in double and rounded
-// to float once (src/run.cpp:306-319); that float is then rounded to bf16, the
-// block's input precision (src/hip/BLAS.hip:32-40), and also written out for the
-// permute kernel.  Only the order of the double additions differs (1e-16).
+// RMSNorm (optional, in rows_to_bf16_kernel) follows the CPU engine bit for bit:
+// the squares are rounded to float and summed in double, 1.0f / sqrtf((float)(ss /
+// H + 1e-5f)) in IEEE float arithmetic, and o = weight * (scale * x) evaluated in
+// double and rounded to float once (src/run.cpp:306-319); that float is then
+// rounded to bf16, the block's input precision (src/hip/BLAS.hip:32-40).  Only the
+// order of the double additions differs (1e-16).
 #pragma once
 #include "common.cuh"
 
@@ -40,16 +42,23 @@ namespace moe {
 constexpr int RB = 64;           // most tokens per routing block (MT = 4); sizes the permute kernels' shared arrays
 constexpr int RMK = 64;          // K chunk: terms the tensor core sums before a round-to-nearest add
 constexpr int RMLD = RMK + 8;    // bf16 per smem row: conflict-free fragment loads
-constexpr int RSTAGES = 3;       // router-matrix stages in flight
 constexpr int RTHREADS = 256;
 
-// Shared memory of one block: RSTAGES x (token tile + router tile), reused for
-// the logits after the K loop, plus the histogram.
+// Stages of the cp.async ring: as many as fit in ~200 KB of shared memory, at most 12.
+template <int NT, int MT>
+__host__ __device__ constexpr int route_tc_stages() {
+    constexpr int stage_bytes = (16 * MT + 32 * NT) * RMLD * 2;
+    constexpr int fit = (200 * 1024) / stage_bytes;
+    return fit > 12 ? 12 : fit;
+}
+
+// Shared memory of one block: the stages (reused for the logits after the K loop)
+// plus the histogram.
 template <int NT, int MT>
 constexpr size_t route_tc_smem_bytes() {
-    size_t tiles = (size_t)RSTAGES * (16 * MT + 32 * NT) * RMLD * 2;
+    size_t tiles = (size_t)route_tc_stages<NT, MT>() * (16 * MT + 32 * NT) * RMLD * 2;
     size_t logits = (size_t)(16 * MT) * (32 * NT) * 4;
-    return (tiles > logits ? tiles : logits) + 256 * sizeof(int) + 16 * MT * sizeof(float);
+    return (tiles > logits ? tiles : logits) + 256 * sizeof(int);
 }
 
 // One warp: v[j] holds the logit of expert lane + 32 j (-inf past E).  Selects
@@ -135,36 +144,112 @@ __device__ __forceinline__ float rms_apply(float x, float w, float scale) {
     return (float)((double)w * ((double)scale * (double)x));
 }
 
+// x f32 [T, H] -> out bf16 [T, H] (round to nearest even, src/hip/BLAS.hip:32-40),
+// with the RMSNorm of src/run.cpp:306-319 applied first when rms_w is given
+// (weight [H], f32 or bf16).  One block per row; the row stays in registers
+// between the sum of squares and the scaling (H <= 8192).
+constexpr int RCAST_THREADS = 256;
+constexpr int RCAST_MAX_VEC = 8;  // float4 per thread: H <= 8192
+
+__global__ void __launch_bounds__(RCAST_THREADS)
+rows_to_bf16_kernel(const float* __restrict__ x, int T, int H, const void* __restrict__ rms_w,
+                    int rms_w_is_f32, uint16_t* __restrict__ out) {
+    __shared__ double s_part[RCAST_THREADS / 32];
+    __shared__ float s_scale;
+    const int t = blockIdx.x, tid = threadIdx.x;
+    if (t >= T)
+        return;
+    const int nvec = H / 4;
+    const float4* row = reinterpret_cast<const float4*>(x + (size_t)t * H);
+    float4 v[RCAST_MAX_VEC];
+#pragma unroll
+    for (int i = 0; i < RCAST_MAX_VEC; i++) {
+        const int k = tid + i * RCAST_THREADS;
+        v[i] = (k < nvec) ? row[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float scale = 1.f;
+    if (rms_w) {
+        // float products summed in double (src/run.cpp:308-311)
+        double ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < RCAST_MAX_VEC; i++) {
+            ss += (double)(v[i].x * v[i].x);
+            ss += (double)(v[i].y * v[i].y);
+            ss += (double)(v[i].z * v[i].z);
+            ss += (double)(v[i].w * v[i].w);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if ((tid & 31) == 0)
+            s_part[tid >> 5] = ss;
+        __syncthreads();
+        if (tid == 0) {
+            double tot = 0.0;
+            for (int w = 0; w < RCAST_THREADS / 32; w++)
+                tot += s_part[w];
+            tot /= (double)H;
+            tot += (double)1e-5f;
+            s_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)tot));
+        }
+        __syncthreads();
+        scale = s_scale;
+    }
+    uint2* orow = reinterpret_cast<uint2*>(out + (size_t)t * H);
+#pragma unroll
+    for (int i = 0; i < RCAST_MAX_VEC; i++) {
+        const int k = tid + i * RCAST_THREADS;
+        if (k < nvec) {
+            float4 q = v[i];
+            if (rms_w) {
+                float w0, w1, w2, w3;
+                if (rms_w_is_f32) {
+                    const float4 wq = reinterpret_cast<const float4*>(rms_w)[k];
+                    w0 = wq.x, w1 = wq.y, w2 = wq.z, w3 = wq.w;
+                } else {
+                    const uint2 wq = reinterpret_cast<const uint2*>(rms_w)[k];
+                    w0 = __uint_as_float(wq.x << 16), w1 = __uint_as_float(wq.x & 0xFFFF0000u);
+                    w2 = __uint_as_float(wq.y << 16), w3 = __uint_as_float(wq.y & 0xFFFF0000u);
+                }
+                q.x = rms_apply(q.x, w0, scale), q.y = rms_apply(q.y, w1, scale);
+                q.z = rms_apply(q.z, w2, scale), q.w = rms_apply(q.w, w3, scale);
+            }
+            orow[k] = make_uint2(pack_bf16x2(q.x, q.y), pack_bf16x2(q.z, q.w));
+        }
+    }
+}
+
 // NT = number of 32-expert tiles (E <= 32 NT), MT = number of 16-token tiles per block.
-//   x            [T, H] f32 or bf16 (the block input, or with `rms_w` the residual stream)
-//   rms_w        optional norm weight [H] (f32 or bf16 by rms_w_is_f32); needs f32 x
-//   xn_out       with rms_w: the normalised rows as bf16 [T, H] (what the block consumes)
-//   score_out    optional [T, E] logits
+//   x          [T, H] bf16 (XF32: f32)      score_out  optional [T, E] logits
+// XF32: the token rows are fp32 and are rounded to bf16 on their way into shared
+// memory, through registers one chunk ahead instead of the cp.async ring (slower:
+// a chunk then costs a global-load latency).  Only the handle-free entry point,
+// which has nowhere to put a bf16 copy of the rows, uses it.
 // Grid: ceil(T / (16 MT)) blocks of RTHREADS threads.
-template <int NT, int MT>
+template <int NT, int MT, bool XF32>
 __global__ void __launch_bounds__(RTHREADS)
-route_tc_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
-                const uint16_t* __restrict__ w_router, const float* __restrict__ b_router, int E, int K,
-                const void* __restrict__ rms_w, int rms_w_is_f32, uint16_t* __restrict__ xn_out,
-                float* __restrict__ score_out, int* __restrict__ topk_i, float* __restrict__ topk_w,
-                int* __restrict__ blk_hist) {
+route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __restrict__ w_router,
+                const float* __restrict__ b_router, int E, int K, float* __restrict__ score_out,
+                int* __restrict__ topk_i, float* __restrict__ topk_w, int* __restrict__ blk_hist) {
+    const uint16_t* x = static_cast<const uint16_t*>(xv);
     constexpr int RBT = 16 * MT;                 // tokens of this block
     constexpr int EP = NT * 32;                  // padded expert count
     constexpr int N_TILES = NT * 4;              // n8 tiles over the experts
     // 8 warps = MT m-tiles x NG expert groups; a warp owns NTW n8 tiles of one m-tile
     constexpr int NG = 8 / MT;
     constexpr int NTW = (N_TILES + NG - 1) / NG;
-    constexpr int STAGE_ELEMS = (RBT + EP) * RMLD;
-    constexpr size_t tiles_b = (size_t)RSTAGES * STAGE_ELEMS * 2;
+    constexpr int S = route_tc_stages<NT, MT>();
+    constexpr int ROWS = RBT + EP;               // rows of a stage: token rows, then router rows
+    constexpr int STAGE_ELEMS = ROWS * RMLD;
+    constexpr size_t tiles_b = (size_t)S * STAGE_ELEMS * 2;
     constexpr size_t lg_b = (size_t)RBT * EP * 4;
-    constexpr int XSEG = (RBT * 8 + RTHREADS - 1) / RTHREADS;  // 16-byte x segments per thread and chunk
-    constexpr int WSEG = EP * 8 / RTHREADS;                    // 16-byte router segments per thread and chunk (= NT)
+    constexpr int SEGS = (ROWS * 8 + RTHREADS - 1) / RTHREADS;  // 16-byte segments per thread and chunk
+    static_assert(S >= 3, "the ring needs at least three stages");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t* tiles = reinterpret_cast<uint16_t*>(smem_raw);
     float* lg = reinterpret_cast<float*>(smem_raw);  // [RBT][EP], reuses the tiles after the K loop
     int* hist = reinterpret_cast<int*>(smem_raw + (tiles_b > lg_b ? tiles_b : lg_b));
-    float* s_scale = reinterpret_cast<float*>(hist + 256);  // [RBT] rmsnorm scales
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
@@ -173,97 +258,61 @@ route_tc_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
     for (int i = tid; i < 256; i += RTHREADS)
         hist[i] = 0;
 
-    const bool normed = rms_w != nullptr;
-    if (normed) {
-        // sum of squares of each row: float products summed in double (src/run.cpp:308-311)
-        for (int r = warp; r < RBT; r += RTHREADS / 32) {
-            double ss = 0.0;
-            if (t0 + r < T) {
-                const float4* row = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)(t0 + r) * H);
-                for (int v = lane; v < H / 4; v += 32) {
-                    const float4 q = row[v];
-                    ss += (double)(q.x * q.x);
-                    ss += (double)(q.y * q.y);
-                    ss += (double)(q.z * q.z);
-                    ss += (double)(q.w * q.w);
-                }
-            }
+    // Source row of every 16-byte segment this thread copies per chunk (fixed for the
+    // whole kernel); rows past the batch / past E are never copied: zeroed once here.
+    const uint16_t* seg_src[SEGS];
+    int seg_dst[SEGS];
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1)
-                ss += __shfl_xor_sync(0xffffffffu, ss, off);
-            if (lane == 0) {
-                ss /= (double)H;
-                ss += (double)1e-5f;
-                s_scale[r] = __fdiv_rn(1.0f, __fsqrt_rn((float)ss));
+    for (int s = 0; s < SEGS; s++) {
+        const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
+        seg_src[s] = nullptr;
+        seg_dst[s] = row * RMLD + sg * 8;
+        if (seg < ROWS * 8) {
+            if (row < RBT) {
+                if (!XF32 && t0 + row < T)
+                    seg_src[s] = x + (size_t)(t0 + row) * H + sg * 8;
+            } else if (row - RBT < E) {
+                seg_src[s] = w_router + (size_t)(row - RBT) * H + sg * 8;
+            }
+            if (!seg_src[s] && !(XF32 && row < RBT)) {
+                for (int st = 0; st < S; st++)
+                    *reinterpret_cast<uint4*>(tiles + st * STAGE_ELEMS + seg_dst[s]) = make_uint4(0, 0, 0, 0);
             }
         }
-        __syncthreads();
     }
-
-    // ---- loads of one chunk
-    auto w_issue = [&](int c) {  // cp.async of router chunk c into its stage
-        uint16_t* ws = tiles + (c % RSTAGES) * STAGE_ELEMS + RBT * RMLD;
+    auto issue = [&](int c) {  // cp.async of chunk c into its stage
+        uint16_t* st = tiles + (c % S) * STAGE_ELEMS;
 #pragma unroll
-        for (int s = 0; s < WSEG; s++) {
-            const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
-            uint16_t* dst = ws + row * RMLD + sg * 8;
-            if (row < E)
-                cp_async_16(dst, w_router + (size_t)row * H + c * RMK + sg * 8);
-            else
-                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
+        for (int s = 0; s < SEGS; s++)
+            if (seg_src[s])
+                cp_async_16(st + seg_dst[s], seg_src[s] + c * RMK);
     };
+
+    // XF32 only: token rows through registers
+    constexpr int XSEG = (RBT * 8 + RTHREADS - 1) / RTHREADS;
     uint4 xr[XSEG];
-    auto x_fetch = [&](int c) {  // token rows of chunk c -> registers (bf16, normed if asked)
+    auto x_fetch = [&](int c) {
 #pragma unroll
         for (int s = 0; s < XSEG; s++) {
             const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
             uint4 q = make_uint4(0, 0, 0, 0);
             if (seg < RBT * 8 && t0 + row < T) {
-                const size_t off = (size_t)(t0 + row) * H + c * RMK + sg * 8;
-                if (x_is_f32) {
-                    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + off);
-                    float4 a = p[0], b = p[1];
-                    if (normed) {
-                        const float sc = s_scale[row];
-                        float w[8];
-                        if (rms_w_is_f32) {
-                            const float4* pw = reinterpret_cast<const float4*>(static_cast<const float*>(rms_w) + c * RMK + sg * 8);
-                            const float4 wa = pw[0], wb = pw[1];
-                            w[0] = wa.x, w[1] = wa.y, w[2] = wa.z, w[3] = wa.w;
-                            w[4] = wb.x, w[5] = wb.y, w[6] = wb.z, w[7] = wb.w;
-                        } else {
-                            const uint4 wq = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(rms_w) + c * RMK + sg * 8);
-                            const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
-#pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                w[2 * i] = __uint_as_float(ww[i] << 16);
-                                w[2 * i + 1] = __uint_as_float(ww[i] & 0xFFFF0000u);
-                            }
-                        }
-                        a.x = rms_apply(a.x, w[0], sc), a.y = rms_apply(a.y, w[1], sc);
-                        a.z = rms_apply(a.z, w[2], sc), a.w = rms_apply(a.w, w[3], sc);
-                        b.x = rms_apply(b.x, w[4], sc), b.y = rms_apply(b.y, w[5], sc);
-                        b.z = rms_apply(b.z, w[6], sc), b.w = rms_apply(b.w, w[7], sc);
-                    }
-                    q = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
-                                   pack_bf16x2(b.z, b.w));
-                    if (normed)
-                        *reinterpret_cast<uint4*>(xn_out + off) = q;
-                } else {
-                    q = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + off);
-                }
+                const float4* p = reinterpret_cast<const float4*>(
+                    static_cast<const float*>(xv) + (size_t)(t0 + row) * H + c * RMK + sg * 8);
+                const float4 a = p[0], b = p[1];
+                q = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
+                               pack_bf16x2(b.z, b.w));
             }
             xr[s] = q;
         }
     };
     auto x_stash = [&](int c) {
-        uint16_t* xs = tiles + (c % RSTAGES) * STAGE_ELEMS;
+        uint16_t* st = tiles + (c % S) * STAGE_ELEMS;
 #pragma unroll
         for (int s = 0; s < XSEG; s++) {
             const int seg = tid + s * RTHREADS, row = seg >> 3, sg = seg & 7;
             if (seg < RBT * 8)
-                *reinterpret_cast<uint4*>(xs + row * RMLD + sg * 8) = xr[s];
+                *reinterpret_cast<uint4*>(st + row * RMLD + sg * 8) = xr[s];
         }
     };
 
@@ -275,28 +324,31 @@ route_tc_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
             run[n][i] = 0.f;
 
     const int n_chunks = H / RMK;  // H is a multiple of 64
-    // prologue: router chunks 0 .. RSTAGES-2 in flight, token chunk 0 in its stage, chunk 1 in registers
 #pragma unroll
-    for (int c = 0; c < RSTAGES - 1; c++) {
+    for (int c = 0; c < S - 1; c++) {
         if (c < n_chunks)
-            w_issue(c);
+            issue(c);
         cp_async_commit();
     }
-    x_fetch(0);
-    x_stash(0);
-    if (n_chunks > 1)
-        x_fetch(1);
+    if (XF32) {
+        x_fetch(0);
+        x_stash(0);
+        if (n_chunks > 1)
+            x_fetch(1);
+    }
     for (int c = 0; c < n_chunks; c++) {
-        cp_async_wait<RSTAGES - 2>();  // this thread's copies of router chunk c have landed
-        __syncthreads();               // everybody's have, token chunk c is stored, chunk c-1 is consumed
-        if (c + RSTAGES - 1 < n_chunks)
-            w_issue(c + RSTAGES - 1);  // into the stage chunk c-1 just left
+        cp_async_wait<S - 2>();  // this thread's copies of chunk c have landed
+        __syncthreads();         // everybody's have, and chunk c-1 is consumed
+        if (c + S - 1 < n_chunks)
+            issue(c + S - 1);    // into the stage chunk c-1 just left
         cp_async_commit();
-        if (c + 1 < n_chunks)
-            x_stash(c + 1);            // its stage was last read for chunk c + 1 - RSTAGES
-        if (c + 2 < n_chunks)
-            x_fetch(c + 2);
-        const uint16_t* xs = tiles + (c % RSTAGES) * STAGE_ELEMS;
+        if (XF32) {
+            if (c + 1 < n_chunks)
+                x_stash(c + 1);  // its stage was last read for chunk c + 1 - S
+            if (c + 2 < n_chunks)
+                x_fetch(c + 2);
+        }
+        const uint16_t* xs = tiles + (c % S) * STAGE_ELEMS;
         const uint16_t* ws = xs + RBT * RMLD;
         float acc[NTW][4];
 #pragma unroll
@@ -304,23 +356,25 @@ route_tc_kernel(const void* __restrict__ x, int x_is_f32, int T, int H,
 #pragma unroll
             for (int i = 0; i < 4; i++)
                 acc[n][i] = 0.f;
+        if (ng * NTW < N_TILES) {
 #pragma unroll
-        for (int kk = 0; kk < RMK / 16; kk++) {
-            uint32_t af[4];
-            const uint16_t* pa = xs + (mb * 16 + g) * RMLD + kk * 16 + 2 * t4;
-            af[0] = *reinterpret_cast<const uint32_t*>(pa);
-            af[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * RMLD);
-            af[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
-            af[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * RMLD + 8);
+            for (int kk = 0; kk < RMK / 16; kk++) {
+                uint32_t af[4];
+                const uint16_t* pa = xs + (mb * 16 + g) * RMLD + kk * 16 + 2 * t4;
+                af[0] = *reinterpret_cast<const uint32_t*>(pa);
+                af[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * RMLD);
+                af[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
+                af[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * RMLD + 8);
 #pragma unroll
-            for (int n = 0; n < NTW; n++) {
-                const int nt = ng * NTW + n;
-                if (nt < N_TILES) {
-                    const uint16_t* pb = ws + (nt * 8 + g) * RMLD + kk * 16 + 2 * t4;
-                    uint32_t bf[2];
-                    bf[0] = *reinterpret_cast<const uint32_t*>(pb);
-                    bf[1] = *reinterpret_cast<const uint32_t*>(pb + 8);
-                    route_mma_16816(acc[n], af, bf);
+                for (int n = 0; n < NTW; n++) {
+                    const int nt = ng * NTW + n;
+                    if (nt < N_TILES) {
+                        const uint16_t* pb = ws + (nt * 8 + g) * RMLD + kk * 16 + 2 * t4;
+                        uint32_t bf[2];
+                        bf[0] = *reinterpret_cast<const uint32_t*>(pb);
+                        bf[1] = *reinterpret_cast<const uint32_t*>(pb + 8);
+                        route_mma_16816(acc[n], af, bf);
+                    }
                 }
             }
         }

@@ -92,6 +92,12 @@ class MoEEngine:
             self.set_experts(layer, a, *(np.ascontiguousarray(x[i:j]) for x in (
                 lw.blocks1, lw.scales1, lw.bias1, lw.blocks2, lw.scales2, lw.bias2)))
 
+    def load_layer_file(self, path: str, file_layer: int, layer: int | None = None):
+        """Router + this rank's expert shard of one layer from a packed expert file
+        (``expert_file.write_expert_file``): the library maps the file itself."""
+        capi.check(self._lib.moe_b200_load_experts_file(
+            self._h, path.encode(), file_layer, file_layer if layer is None else layer), self._h, self._lib)
+
     # -- the block --------------------------------------------------------
     def forward(self, layer: int, t: torch.Tensor, out: torch.Tensor | None = None,
                 accumulate: bool = False, side: bool = False, stream=None):

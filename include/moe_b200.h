@@ -117,6 +117,26 @@ moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int fir
                                            const float* bias1, const uint8_t* blocks2,
                                            const uint8_t* scales2, const float* bias2);
 
+/* Packed expert file: the experts and routers of a model as the checkpoint has
+ * them (e2m1 blocks + e8m0 scales + fp32 biases, expert-major, one page-aligned
+ * record per (layer, expert)), written by gpt-oss-amd_b200/expert_file.py.
+ * Replaces, for the MoE weights, the fp32 .bin of
+ * tools/model_export/gpt-oss-20b/export_model_bin.py:95-133 and the loader's
+ * fp32 -> bf16 streaming conversion (src/model.cpp:8-56,141-186); everything
+ * else stays in the engine's .bin (src/run.cpp:196-235).
+ * moe_b200_expert_file_info reads and validates the header (pure host code; any
+ * output pointer may be NULL).  moe_b200_load_experts_file maps the file and
+ * uploads layer `file_layer` of it into layer `layer` of the handle: the router
+ * and the records of THIS rank's expert shard only -- other ranks' records are
+ * never touched.  The file's hidden_dim, intermediate_dim, n_experts and
+ * experts_per_token must equal the handle's. */
+moe_b200_status moe_b200_expert_file_info(const char* path, int* n_layers, int* n_experts,
+                                          int* hidden_dim, int* intermediate_dim,
+                                          int* experts_per_token, float* swiglu_limit,
+                                          unsigned long long* file_bytes);
+moe_b200_status moe_b200_load_experts_file(moe_b200_handle h, const char* path, int file_layer,
+                                           int layer);
+
 /* The MoE block of one layer for n_tokens rows (src/forward.cpp:317-514, and
  * :515-992 when ep_size > 1).
  *   t            device, [n_tokens, H], f32 or bf16 (f32 is rounded to bf16 on
