@@ -7,5 +7,5 @@ generators of the benchmark configurations (``synth``), the writer of the packed
 expert file the library loads (``expert_file``) and the build script.
 """
 from . import capi, expert_file, synth  # noqa: F401
-from .moe import MoEEngine, mxfp4_unpack  # noqa: F401
+from .moe import MoEEngine, RequestQueue, TokenBatcher, mxfp4_unpack  # noqa: F401
 from .synth import LayerWeights, MoEShape, make_layer, make_tokens  # noqa: F401

@@ -29,6 +29,9 @@ SYMBOLS = [
     "moe_b200_last_intermediate", "moe_b200_route_noalloc",
     "moe_b200_ep_peer_export", "moe_b200_ep_peer_enable", "moe_b200_ep_peer_sequence",
     "moe_b200_ep_peer_resync", "moe_b200_expert_file_info", "moe_b200_load_experts_file",
+    "moe_b200_request_queue_create", "moe_b200_request_queue_destroy", "moe_b200_batcher_create",
+    "moe_b200_batcher_destroy", "moe_b200_batcher_begin_step", "moe_b200_batcher_end_step",
+    "moe_b200_batcher_stats",
 ]
 N_STAGES = 11
 STAGE_NAMES = ["route", "plan", "permute", "dispatch", "regroup", "gemm1", "gemm2", "return",
@@ -91,6 +94,18 @@ def _bind(L: ctypes.CDLL) -> ctypes.CDLL:
     L.moe_b200_expert_file_info.argtypes = [ctypes.c_char_p, ip, ip, ip, ip, ip, fp,
                                             ctypes.POINTER(ctypes.c_ulonglong)]
     L.moe_b200_load_experts_file.argtypes = [vp, ctypes.c_char_p, ci, ci]
+    ipp = ctypes.POINTER(ip)
+    llp = ctypes.POINTER(ctypes.c_longlong)
+    L.moe_b200_request_queue_create.argtypes = [ci, ipp, ip, ipp, ci, ctypes.POINTER(vp)]
+    L.moe_b200_request_queue_destroy.argtypes = [vp]
+    L.moe_b200_request_queue_destroy.restype = None
+    L.moe_b200_batcher_create.argtypes = [vp, ci, ci, ctypes.POINTER(vp)]
+    L.moe_b200_batcher_destroy.argtypes = [vp]
+    L.moe_b200_batcher_destroy.restype = None
+    L.moe_b200_batcher_begin_step.argtypes = [vp, ip, ip, ip, ip]
+    L.moe_b200_batcher_end_step.argtypes = [vp, ip]
+    L.moe_b200_batcher_stats.argtypes = [vp, llp, llp, llp]
+    L.moe_b200_batcher_stats.restype = None
     L.moe_b200_profile.argtypes = [vp, ci]
     L.moe_b200_profile_read.argtypes = [vp, ci, ctypes.POINTER(ctypes.c_float)]
     return L

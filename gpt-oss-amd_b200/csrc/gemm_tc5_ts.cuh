@@ -61,7 +61,12 @@ constexpr int G = 4;                         // decode groups of four warps
 //   SA  A slots (tensor memory)   SB  activation slots   WS  packed slots   NB  barrier pairs
 // SA and WS are multiples of G, so the successive fills of a slot are handled by one
 // group in program order (an mbarrier parity wait cannot tell phase n from phase n-2).
-constexpr int SA = 8, SB = 8, NB = 8, WS = 12;
+// The packed ring is what keeps HBM busy: a slot's round trip is the memory latency
+// plus two warp wake-ups (decode group, producer), several microseconds under load,
+// so the ring is as deep as shared memory allows (28 x 4352 B = 119 KB in flight per
+// SM; with 52 KB the kernel ran at a third of the HBM rate whatever else changed).
+// The activation tiles are small and come from L2: four slots are enough.
+constexpr int SA = 8, SB = 4, NB = 8, WS = 28;
 constexpr int SETS = 2;                      // accumulator sets: the MMAs of item i+1 overlap the epilogue of item i
 constexpr int TMEM_A0 = SETS * BN;           // first tensor-memory column of the A slots
 constexpr int TMEM_COLS = 512;

@@ -11,6 +11,7 @@
 #include <string>
 #include <vector>
 
+#include "batcher.hpp"
 #include "common.cuh"
 #include "ep.cuh"
 #include "expert_file.hpp"
@@ -42,6 +43,13 @@ struct LayerWeights {
 };
 
 }  // namespace
+
+struct moe_b200_request_queue_s {
+    moe::sched::RequestQueue q;
+};
+struct moe_b200_batcher_s {
+    moe::sched::Batcher b;
+};
 
 struct moe_b200_handle_s {
     moe_b200_config cfg{};
@@ -1168,6 +1176,75 @@ moe_b200_status moe_b200_ep_peer_resync(moe_b200_handle h, int sequence) {
     CU_TRY(h, cudaMemset(h->ep.tickets, 0, 2 * sizeof(int)));
     h->ep.seq = sequence;
     return MOE_B200_OK;
+}
+
+moe_b200_status moe_b200_request_queue_create(int n_requests, const int* const* prompt_tokens,
+                                              const int* prompt_lens, int* const* output_tokens,
+                                              int max_seq_len, moe_b200_request_queue* out) {
+    if (!out)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "null argument");
+    *out = nullptr;
+    if (n_requests < 0 || max_seq_len <= 0 || (n_requests > 0 && (!prompt_tokens || !prompt_lens)))
+        return fail(nullptr, MOE_B200_ERR_INVALID, "bad request queue arguments");
+    for (int r = 0; r < n_requests; r++)
+        if (prompt_lens[r] < 1 || !prompt_tokens[r])  // src/getp/run.cpp:505-508
+            return fail(nullptr, MOE_B200_ERR_INVALID,
+                        "request " + std::to_string(r) + " has no prompt token");
+    moe_b200_request_queue q = new (std::nothrow) moe_b200_request_queue_s();
+    if (!q)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "out of host memory");
+    q->q.n_requests = n_requests;
+    q->q.max_seq_len = max_seq_len;
+    q->q.prompt_tokens = prompt_tokens;
+    q->q.prompt_lens = prompt_lens;
+    q->q.output_tokens = output_tokens;
+    *out = q;
+    return MOE_B200_OK;
+}
+
+void moe_b200_request_queue_destroy(moe_b200_request_queue q) { delete q; }
+
+moe_b200_status moe_b200_batcher_create(moe_b200_request_queue q, int n_slots, int continuous,
+                                        moe_b200_batcher* out) {
+    if (!q || !out || n_slots <= 0)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "bad batcher arguments");
+    moe_b200_batcher b = new (std::nothrow) moe_b200_batcher_s();
+    if (!b)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "out of host memory");
+    b->b.q = &q->q;
+    b->b.n_slots = n_slots;
+    b->b.continuous = continuous != 0;
+    b->b.slots.assign(n_slots, moe::sched::Slot());
+    b->b.row_slot.reserve(n_slots);
+    *out = b;
+    return MOE_B200_OK;
+}
+
+void moe_b200_batcher_destroy(moe_b200_batcher b) { delete b; }
+
+int moe_b200_batcher_begin_step(moe_b200_batcher b, int* tokens, int* positions, int* slots,
+                                int* needs_sample) {
+    if (!b || !tokens || !positions || !slots || b->b.step_open)
+        return -1;
+    return moe::sched::begin_step(b->b, tokens, positions, slots, needs_sample);
+}
+
+moe_b200_status moe_b200_batcher_end_step(moe_b200_batcher b, const int* sampled) {
+    if (!b || !sampled || !b->b.step_open)
+        return fail(nullptr, MOE_B200_ERR_INVALID, "end_step without a step in flight");
+    moe::sched::end_step(b->b, sampled);
+    return MOE_B200_OK;
+}
+
+void moe_b200_batcher_stats(moe_b200_batcher b, long long* steps, long long* rows, long long* tokens_out) {
+    if (!b)
+        return;
+    if (steps)
+        *steps = b->b.steps;
+    if (rows)
+        *rows = b->b.rows;
+    if (tokens_out)
+        *tokens_out = b->b.tokens_out;
 }
 
 size_t moe_b200_device_bytes(moe_b200_handle h) { return h ? h->device_bytes : 0; }

@@ -44,12 +44,16 @@ constexpr int RMK = 64;          // K chunk: terms the tensor core sums before a
 constexpr int RMLD = RMK + 8;    // bf16 per smem row: conflict-free fragment loads
 constexpr int RTHREADS = 256;
 
-// Stages of the cp.async ring: as many as fit in ~200 KB of shared memory, at most 12.
+// Stages of the cp.async ring.  Short blocks (small batches: at most a block or two per
+// SM) take as many as fit in ~200 KB of shared memory, at most 12; the 64-token blocks
+// of large batches stay under half of it so that two blocks share an SM and a batch of
+// 16384 tokens (256 blocks) runs as one wave.
 template <int NT, int MT>
 __host__ __device__ constexpr int route_tc_stages() {
     constexpr int stage_bytes = (16 * MT + 32 * NT) * RMLD * 2;
-    constexpr int fit = (200 * 1024) / stage_bytes;
-    return fit > 12 ? 12 : fit;
+    constexpr int budget = (MT == 4 ? 100 : 200) * 1024;
+    constexpr int fit = budget / stage_bytes;
+    return fit > 12 ? 12 : (fit < 3 ? 3 : fit);
 }
 
 // Shared memory of one block: the stages (reused for the logits after the K loop)
@@ -280,12 +284,23 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
             }
         }
     }
-    auto issue = [&](int c) {  // cp.async of chunk c into its stage
+    // Every block walks the K chunks in its own rotation: all blocks read the same
+    // router rows, and in lock step they would all ask the same L2 lines at once.
+    const int n_chunks = H / RMK;  // H is a multiple of 64
+    const int c_rot = (int)((blockIdx.x * 7u) % (unsigned)n_chunks);
+    auto chunk_col = [&](int c) {
+        int k = c + c_rot;
+        if (k >= n_chunks)
+            k -= n_chunks;
+        return k * RMK;
+    };
+    auto issue = [&](int c) {  // cp.async of the c-th chunk of this block into its stage
         uint16_t* st = tiles + (c % S) * STAGE_ELEMS;
+        const int col = chunk_col(c);
 #pragma unroll
         for (int s = 0; s < SEGS; s++)
             if (seg_src[s])
-                cp_async_16(st + seg_dst[s], seg_src[s] + c * RMK);
+                cp_async_16(st + seg_dst[s], seg_src[s] + col);
     };
 
     // XF32 only: token rows through registers
@@ -298,7 +313,7 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
             uint4 q = make_uint4(0, 0, 0, 0);
             if (seg < RBT * 8 && t0 + row < T) {
                 const float4* p = reinterpret_cast<const float4*>(
-                    static_cast<const float*>(xv) + (size_t)(t0 + row) * H + c * RMK + sg * 8);
+                    static_cast<const float*>(xv) + (size_t)(t0 + row) * H + chunk_col(c) + sg * 8);
                 const float4 a = p[0], b = p[1];
                 q = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y),
                                pack_bf16x2(b.z, b.w));
@@ -323,7 +338,6 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
         for (int i = 0; i < 4; i++)
             run[n][i] = 0.f;
 
-    const int n_chunks = H / RMK;  // H is a multiple of 64
 #pragma unroll
     for (int c = 0; c < S - 1; c++) {
         if (c < n_chunks)

@@ -246,6 +246,72 @@ class MoEEngine:
         return out
 
 
+class RequestQueue:
+    """The requests of a serving run, shared by the batchers of all ranks: encoded
+    prompts in, generated tokens out (the Requests buffers of src/getp/eval.cpp:10-40)."""
+
+    def __init__(self, prompts: list, max_seq_len: int):
+        self.n = len(prompts)
+        self.max_seq_len = max_seq_len
+        self._prompts = [np.ascontiguousarray(p, dtype=np.int32) for p in prompts]
+        self._lens = np.array([len(p) for p in self._prompts], dtype=np.int32)
+        self.outputs = np.zeros((max(self.n, 1), max_seq_len + 1), dtype=np.int32)
+        ip = ctypes.POINTER(ctypes.c_int)
+        self._pp = (ip * max(self.n, 1))(*[p.ctypes.data_as(ip) for p in self._prompts])
+        self._op = (ip * max(self.n, 1))(*[self.outputs[r].ctypes.data_as(ip) for r in range(max(self.n, 1))])
+        h = ctypes.c_void_p()
+        capi.check(capi.lib().moe_b200_request_queue_create(
+            self.n, self._pp, self._lens.ctypes.data_as(ip), self._op, max_seq_len, ctypes.byref(h)))
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            capi.lib().moe_b200_request_queue_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+
+class TokenBatcher:
+    """One rank's view of the serving loop: which (token, position, slot) rows go into
+    the next forward() (moe_b200_batcher_*; src/getp/run.cpp:573-617,661-736)."""
+
+    def __init__(self, queue: RequestQueue, n_slots: int, continuous: bool = True):
+        self.queue, self.n_slots = queue, n_slots
+        h = ctypes.c_void_p()
+        capi.check(capi.lib().moe_b200_batcher_create(queue._h, n_slots, int(continuous), ctypes.byref(h)))
+        self._h = h
+        self._buf = [np.zeros(n_slots, dtype=np.int32) for _ in range(4)]
+
+    def begin_step(self):
+        """-> (tokens, positions, slots, needs_sample) arrays of the step's rows, or None."""
+        ip = ctypes.POINTER(ctypes.c_int)
+        n = capi.lib().moe_b200_batcher_begin_step(self._h, *[b.ctypes.data_as(ip) for b in self._buf])
+        if n < 0:
+            raise RuntimeError("begin_step while a step is in flight")
+        if n == 0:
+            return None
+        return tuple(b[:n].copy() for b in self._buf)
+
+    def end_step(self, sampled):
+        s = np.ascontiguousarray(sampled, dtype=np.int32)
+        capi.check(capi.lib().moe_b200_batcher_end_step(self._h, s.ctypes.data_as(ctypes.POINTER(ctypes.c_int))))
+
+    def stats(self) -> dict:
+        v = [ctypes.c_longlong() for _ in range(3)]
+        capi.lib().moe_b200_batcher_stats(self._h, *[ctypes.byref(x) for x in v])
+        return {"steps": v[0].value, "rows": v[1].value, "tokens_out": v[2].value}
+
+    def close(self):
+        if getattr(self, "_h", None):
+            capi.lib().moe_b200_batcher_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+
 def mxfp4_unpack(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """blocks CUDA u8 [..., G, 16], scales CUDA u8 [..., G] -> bf16 bits (int16) [..., 32 G]."""
     assert blocks.is_cuda and scales.is_cuda and blocks.dtype == torch.uint8

@@ -221,6 +221,46 @@ moe_b200_status moe_b200_ep_peer_resync(moe_b200_handle h, int sequence);
 void moe_b200_ep_plan(int n_experts, int ep_size, int ep_rank, const int* cnt_all, int* send_cnt,
                       int* send_off, int* recv_cnt, int* recv_off);
 
+/* Token grouping of the serving loop (pure host code, no GPU needed): which
+ * (sequence, position) rows go into the next forward() call.  Replaces the
+ * static batches of inference() (src/getp/run.cpp:661-736) and the per-step
+ * compaction of generate() (src/getp/run.cpp:573-617).  The reference steps a
+ * batch until EVERY sequence of it has finished, so the rows per call -- the T
+ * of the MoE block -- decay; with `continuous` != 0 a slot whose sequence
+ * finished is refilled at once from the shared queue and T stays at n_slots
+ * until the queue drains.  continuous == 0 reproduces the reference row for row.
+ *
+ * One queue is shared by all ranks (threads) of a process, one batcher per rank.
+ * prompt_tokens[r] / prompt_lens[r] are request r's encoded prompt (>= 1
+ * token); output_tokens[r] (optional) receives its generated tokens and a
+ * closing -1, max_seq_len + 1 ints (the layout of Requests.tok_gens,
+ * src/getp/eval.cpp:10-40).  The arrays stay owned by the caller.
+ *
+ * A step: begin_step fills tokens / positions / slots (the batch_tokens,
+ * batch_positions, batch_indices arguments of forward(), src/forward.cpp:202-204;
+ * a slot is the sequence's KV-cache row and starts again at position 0 when it
+ * is refilled) and optionally needs_sample (1 where the row has reached the end
+ * of its prompt), each n_slots ints, and returns the number of rows, 0 when all
+ * requests are done, -1 on misuse.  After forward() and sampling, end_step takes
+ * the sampled token per row (ignored where the prompt still supplies the next
+ * token) and applies the reference's rules (src/getp/run.cpp:547-571: tokens
+ * 199999 / 200002 or position + 1 >= max_seq_len end a sequence). */
+typedef struct moe_b200_request_queue_s* moe_b200_request_queue;
+typedef struct moe_b200_batcher_s* moe_b200_batcher;
+moe_b200_status moe_b200_request_queue_create(int n_requests, const int* const* prompt_tokens,
+                                              const int* prompt_lens, int* const* output_tokens,
+                                              int max_seq_len, moe_b200_request_queue* out);
+void moe_b200_request_queue_destroy(moe_b200_request_queue q);
+moe_b200_status moe_b200_batcher_create(moe_b200_request_queue q, int n_slots, int continuous,
+                                        moe_b200_batcher* out);
+void moe_b200_batcher_destroy(moe_b200_batcher b);
+int moe_b200_batcher_begin_step(moe_b200_batcher b, int* tokens, int* positions, int* slots,
+                                int* needs_sample);
+moe_b200_status moe_b200_batcher_end_step(moe_b200_batcher b, const int* sampled);
+/* Forward calls made, rows they carried in total, tokens generated (any pointer may be NULL). */
+void moe_b200_batcher_stats(moe_b200_batcher b, long long* steps, long long* rows,
+                            long long* tokens_out);
+
 /* Bytes of device memory the handle holds (weights + workspace). */
 size_t moe_b200_device_bytes(moe_b200_handle h);
 /* Text of the last error on this handle (or of the last failed create when h
@@ -302,7 +342,7 @@ moe_b200_status moe_b200_last_intermediate(moe_b200_handle h, int n_tokens, uint
  * handed.  The call needs no handle and creates nothing: router GEMM + bias,
  * top-k, softmax and the per-expert histogram / offsets run with their scratch
  * (the per-block histograms) in a fixed array inside the library image, about
- * 0.5 MB, which every GPU that loads the library holds until the process exits.
+ * 0.26 MB, which every GPU that loads the library holds until the process exits.
  *
  *   t                  device [n_tokens, hidden_dim], f32 or bf16
  *   w_router_bf16      device bf16 [n_experts, hidden_dim];  b_router device f32 [n_experts]

@@ -6,7 +6,7 @@ to its own pools at warm-up and cannot afford the device-wide synchronisation
 of cudaMalloc between decode steps, or a host application that only lets a
 plug-in work on buffers it passes in.  For them the library has one entry point
 that needs no handle: the per-block histograms the routing kernels use as
-scratch live in a fixed array in the library image (about 0.5 MB per GPU, at
+scratch live in a fixed array in the library image (about 0.26 MB per GPU, at
 most 2048 tokens and 256 experts per call).
 
 This test calls it through the C ABI twice in a row on different batches --
