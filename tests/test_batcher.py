@@ -87,14 +87,11 @@ def drive(batcher, queue_prompts, slot_request=None):
     return log
 
 
-_next_guess = {}
-
-
 def batcher_request_of(batcher, slot, slot_req, prompts, first_token):
     """Requests are handed out in order from one shared counter; with a single batcher
     the k-th sequence started is request k."""
-    k = _next_guess.get(id(batcher), 0)
-    _next_guess[id(batcher)] = k + 1
+    k = getattr(batcher, "_started", 0)
+    batcher._started = k + 1
     assert int(prompts[k][0]) == first_token
     return k
 
