@@ -278,8 +278,8 @@ class Bench:
             achieved = alg / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None
             peak, unit = peaks["hbm_gbs"], "GB/s"
         # the library picks the kernel from the rows per local expert (pick_bn in csrc/moe_b200.cu)
-        small = (T_local * K) // max(eng.n_local, 1) <= 96
-        kernel = "tc5::swp::expert_gemm_swap_kernel<0>" if small else "tc5::pair::expert_gemm_pair_kernel<0>"
+        small = (T_local * K) // max(eng.n_local, 1) <= 64
+        kernel = "tc5::ts::expert_gemm_ts_kernel<0>" if small else "tc5::pair::expert_gemm_pair_kernel<0>"
         cap = NCU_TRAFFIC.get(name) if (world == 1 and T_total == WORKLOADS[name]["T"]) else None
         res["roofline"] = {"kernel": kernel + " (gate/up GEMM + SwiGLU)", "bound": wl["bound"],
                            "achieved": achieved, "peak": peak, "unit": unit,

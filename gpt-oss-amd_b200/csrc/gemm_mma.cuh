@@ -1,7 +1,7 @@
 // Grouped expert GEMMs on warp-level mma.sync -- the CROSS-CHECK implementation.
 //
 // Same inputs, outputs, weight layout and rounding points as the tcgen05
-// kernels (gemm_tc5_pair.cuh, gemm_tc5_swap.cuh), written as plainly as possible
+// kernels (gemm_tc5_pair.cuh, gemm_tc5_ts.cuh), written as plainly as possible
 // (single-buffered, no TMA, no tensor memory) so that the two can be compared on
 // the device at sizes where the CPU oracle is too slow.  Compiled only into the
 // test-aids build of the library (-DMOE_B200_TEST_AIDS), where

@@ -26,10 +26,21 @@
 // carries only the packed bytes and the small activation tile.
 //
 // One persistent CTA per SM walks work items (expert, 128-row weight tile, tile
-// of up to 128 token rows).  Rings:
-//   W ring   packed MXFP4 chunks in shared memory (bulk copies; covers HBM latency)
-//   A ring   SA slots of 32 tensor-memory columns (decoded weights)
-//   B ring   activation tiles in shared memory (TMA, no multicast)
+// of up to 64 token rows).  A pipeline STEP covers CS = 3 chunks of 64 K-columns
+// (192 columns, 13 KB of packed weights: one bulk copy, the chunks of a weight
+// tile are contiguous): every hand-off between the roles -- a barrier wait, an
+// arrival, a commit -- costs a few hundred cycles whatever it carries, and with one
+// chunk per step the MMA-issuing warp's wait / issue / commit chain alone held the
+// kernel at a third of the HBM rate (measured: removing the decode arithmetic, the
+// tensor-memory stores and three of the four MMAs changed the time by 15 %).  Rings:
+//   W ring   packed MXFP4 steps in shared memory (bulk copies; covers HBM latency)
+//   A ring   SA slots of 96 tensor-memory columns (decoded weights)
+//   B ring   activation tiles in shared memory (TMA, no multicast), handed out in
+//            units of 12 KB: a step of an item with up to 32 token rows takes one
+//            unit, with up to 64 rows two.  A TMA load takes ~2000 cycles to land, so
+//            what matters is how many steps are in flight: eight for the usual
+//            decode-shaped item (with four the kernel waited for activations, not
+//            for weights)
 // and NB barrier pairs indexed by the step number: full[i % NB] collects the
 // decode warps' arrivals and the TMA bytes of step i, empty[i % NB] is signalled
 // by tcgen05.commit when the MMAs of step i are done.
@@ -52,44 +63,47 @@ namespace moe {
 namespace tc5 {
 namespace ts {
 
-constexpr int BN = 128;                      // most token rows per work item (UMMA N)
-constexpr int B_SLOT_BYTES = BN * 128;       // 128 rows x 64 bf16, SW128
-constexpr int A_SLOT_COLS = KSTAGE / 2;      // decoded tile in tensor memory: 128 lanes x 32 columns of bf16x2
+constexpr int BN = 64;                       // most token rows per work item (UMMA N)
+constexpr int CS = STEP_CHUNKS;              // chunks of 64 K-columns per pipeline step
+constexpr int B_UNIT_BYTES = CS * 32 * 128;  // activation tiles of one step for 32 token rows (32 rows x 64 bf16 per chunk, SW128)
+constexpr int SBU = 8;                       // units in the B ring
+constexpr int W_SLOT_BYTES = CS * CHUNK_BYTES;
+constexpr int A_SUB_COLS = KSTAGE / 2;       // one decoded chunk in tensor memory: 128 lanes x 32 columns of bf16x2
+constexpr int A_SLOT_COLS = CS * A_SUB_COLS;
 constexpr int MMA_WARP = 2;
 constexpr int DEQ_WARP0 = 3;
 constexpr int G = 4;                         // decode groups of four warps
 //   SA  A slots (tensor memory)   SB  activation slots   WS  packed slots   NB  barrier pairs
 // SA and WS are multiples of G, so the successive fills of a slot are handled by one
 // group in program order (an mbarrier parity wait cannot tell phase n from phase n-2).
-// The packed ring is what keeps HBM busy: a slot's round trip is the memory latency
-// plus two warp wake-ups (decode group, producer), several microseconds under load,
-// so the ring is as deep as shared memory allows (28 x 4352 B = 119 KB in flight per
-// SM; with 52 KB the kernel ran at a third of the HBM rate whatever else changed).
-// The activation tiles are small and come from L2: four slots are enough.
-constexpr int SA = 8, SB = 4, NB = 8, WS = 28;
+constexpr int SA = 4, NB = 8, WS = 8;
 constexpr int SETS = 2;                      // accumulator sets: the MMAs of item i+1 overlap the epilogue of item i
 constexpr int TMEM_A0 = SETS * BN;           // first tensor-memory column of the A slots
 constexpr int TMEM_COLS = 512;
 static_assert(TMEM_A0 + SA * A_SLOT_COLS <= TMEM_COLS, "tensor memory");
-static_assert(SA % G == 0 && WS % G == 0 && NB % SA == 0 && NB % SB == 0 && NB % G == 0,
+static_assert(SA % G == 0 && WS % G == 0 && NB % SA == 0 && NB % G == 0 && NB >= SBU,
               "a slot's successive fills must belong to one decode group");
 constexpr int EPI_WARP0 = DEQ_WARP0 + 4 * G;
 constexpr int N_THREADS = (EPI_WARP0 + 4) * 32;  // 736
 constexpr int MAX_LOCAL_EXPERTS = 256;
 constexpr int EPI_STAGE_BYTES = 2048;
 constexpr int N_BARRIERS = 2 * WS + 2 * NB + 2 * SETS;
-constexpr int SMEM_BYTES = SB * B_SLOT_BYTES + WS * CHUNK_BYTES + 4 * EPI_STAGE_BYTES + N_BARRIERS * 8 +
+constexpr int SMEM_BYTES = SBU * B_UNIT_BYTES + WS * W_SLOT_BYTES + 4 * EPI_STAGE_BYTES + N_BARRIERS * 8 +
                            (MAX_LOCAL_EXPERTS + 1) * 3 * 4 + 64 + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 
 // D[tmem] (+)= A[tmem] . B[smem desc]^T: A is 128 lanes x 8 columns (16 bf16 of K per lane).
-__device__ __forceinline__ void umma_ts_bf16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                             uint32_t idesc, uint32_t accumulate) {
+// The shared-memory descriptor comes as its two 32-bit halves: stepping through a tile
+// only changes the start-address field in the low half, one 32-bit add per MMA in the
+// issuing warp's chain instead of a 64-bit one.
+__device__ __forceinline__ void umma_ts_bf16(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo,
+                                             uint32_t b_desc_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp writes lane (taddr.lane + i).
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t a[32]) {
@@ -109,7 +123,7 @@ struct TileInfo {
     int e;        // local expert
     int mt;       // 128-row weight tile
     int row0;     // first token row of the item
-    int valid_n;  // token rows of the item (1..128)
+    int valid_n;  // token rows of the item (1..64)
     int n_mma;    // rows the MMA computes (a multiple of 32)
     int box_idx;  // TMA box: 32 << box_idx rows
 };
@@ -140,7 +154,7 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int m_tiles, const Til
     ti.row0 = tt.off[lo] + n0;
     ti.valid_n = min(BN, tt.cnt[lo] - n0);
     ti.n_mma = max(32, (ti.valid_n + 31) & ~31);
-    ti.box_idx = ti.n_mma <= 32 ? 0 : ti.n_mma <= 64 ? 1 : 2;
+    ti.box_idx = ti.n_mma <= 32 ? 0 : 1;
     return ti;
 }
 
@@ -161,8 +175,8 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     unsigned char* b_ring = smem;
-    unsigned char* w_ring = b_ring + SB * B_SLOT_BYTES;
-    unsigned char* epi_stage = w_ring + WS * CHUNK_BYTES;
+    unsigned char* w_ring = b_ring + SBU * B_UNIT_BYTES;
+    unsigned char* epi_stage = w_ring + WS * W_SLOT_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + 4 * EPI_STAGE_BYTES);
     int* s_tables = reinterpret_cast<int*>(bars + N_BARRIERS);
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(s_tables + 3 * (MAX_LOCAL_EXPERTS + 1));
@@ -211,6 +225,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
     tt.tile_start = s_tables + 2 * (MAX_LOCAL_EXPERTS + 1);
 
     const int total_tiles = tt.tile_start[E] * m_tiles;
+    const int n_steps = (k_stages + CS - 1) / CS;  // pipeline steps per work item; the last may hold fewer chunks
 
     if (warp == 0) {
         // ------------------------- packed-weight producer ----------------------
@@ -218,17 +233,24 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             int s = 0, armed = 0;
             uint32_t ph = 0;
             bool ok = true;
+            int wstep = 0;
+            (void)wstep;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileInfo ti = decode_tile(tile, m_tiles, tt, E);
                 const uint8_t* wsrc = chunks + (size_t)ti.e * expert_stride +
                                       (size_t)ti.mt * k_stages * CHUNK_BYTES;
-                for (int ks = 0; ks < k_stages; ks++) {
+                for (int st = 0; st < n_steps; st++) {
                     ok = mbar_wait(bar_w_empty(s), ph ^ 1u, status, DS_TIMEOUT_EMPTY, abort_flag);
                     if (!ok)
                         break;
-                    mbar_expect_tx(bar_w_full(s), (uint32_t)CHUNK_BYTES);
-                    bulk_load(smem_u32(w_ring + s * CHUNK_BYTES), wsrc + (size_t)ks * CHUNK_BYTES,
-                              CHUNK_BYTES, bar_w_full(s));
+                    TRACE(wstep, 0);
+                    // the chunks of a weight tile are contiguous: one copy per step
+                    const uint32_t bytes = (uint32_t)(min(CS, k_stages - st * CS) * CHUNK_BYTES);
+                    mbar_expect_tx(bar_w_full(s), bytes);
+                    bulk_load(smem_u32(w_ring + s * W_SLOT_BYTES), wsrc + (size_t)st * W_SLOT_BYTES, bytes,
+                              bar_w_full(s));
+                    TRACE(wstep, 1);
+                    ++wstep;
                     armed = min(armed + 1, WS);
                     RING_ADVANCE(s, ph, WS);
                 }
@@ -246,9 +268,12 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
     } else if (warp == 1) {
         // ------------------------- activation-tile producer --------------------
         if (lane == 0) {
-            // step i: slot i % SB, barrier i % NB; the slot is free when step i - SB is done
-            int i = 0, sb = 0, nb = 0, eb = 0;
-            uint32_t phe = 0;
+            // step i: barrier i % NB; its tiles take one or two units of the B ring (one copy:
+            // a 3-d box of CS chunks).  Before a step is issued, step i - Q must be done, where Q
+            // is how many steps the ring is sure to hold: SBU while the last SBU steps all took
+            // one unit, SBU / 2 otherwise.  Steps finish in order, so the producer consumes the
+            // empty barriers in step order.
+            int i = 0, nb = 0, bu = 0, waited = 0, ones_run = 0;
             bool ok = true;
             if (MODE == 0 && pio.wait_flags) {
                 // expert-parallel peer mode: the rows of this GEMM are stored by the other
@@ -263,18 +288,26 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             }
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const TileInfo ti = decode_tile(tile, m_tiles, tt, E);
-                for (int ks = 0; ks < k_stages; ks++, i++) {
-                    if (i >= SB) {
-                        ok = mbar_wait(bar_empty(eb), phe, status, DS_TIMEOUT_EMPTY, abort_flag);
-                        if (!ok)
-                            break;
-                        RING_ADVANCE(eb, phe, NB);
+                const int need = ti.n_mma >> 5;  // units per step: 1 or 2
+                for (int st = 0; st < n_steps; st++, i++) {
+                    if (need == 2 && (bu & 1))
+                        bu = (bu + 1) & (SBU - 1);
+                    ones_run = (need == 1) ? ones_run + 1 : 0;
+                    const int last = i - (ones_run > SBU ? SBU : SBU / 2);
+                    while (ok && waited <= last) {
+                        ok = mbar_wait(bar_empty(waited % NB), (uint32_t)(waited / NB) & 1u, status,
+                                       DS_TIMEOUT_EMPTY, abort_flag);
+                        waited++;
                     }
-                    mbar_expect_tx(bar_full(nb), (uint32_t)(32 << ti.box_idx) * 128u);
-                    tma_load_2d(smem_u32(b_ring + sb * B_SLOT_BYTES), &maps.box[ti.box_idx],
-                                bar_full(nb), ks * KSTAGE, ti.row0);
-                    if (++sb == SB)
-                        sb = 0;
+                    if (!ok)
+                        break;
+                    TRACE(i, 2);
+                    // the whole box is delivered (chunks past the end of K arrive as zeros)
+                    mbar_expect_tx(bar_full(nb), (uint32_t)(CS * ti.n_mma) * 128u);
+                    tma_load_3d(smem_u32(b_ring + bu * B_UNIT_BYTES), &maps.box3[ti.box_idx], bar_full(nb), 0,
+                                ti.row0, st * CS);
+                    TRACE(i, 3);
+                    bu = (bu + need) & (SBU - 1);
                     if (++nb == NB)
                         nb = 0;
                 }
@@ -290,14 +323,15 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issuer ----------------------------
-        // The whole warp runs the loop with no lane-divergent code but the elected
-        // issue; the barrier of the NEXT step is tested before the MMAs of this step
-        // are issued, so that its latency overlaps the issue.
-        int sa = 0, sb = 0, nb = 0;  // step i: A slot i % SA, B slot i % SB, barriers i % NB
+        // The whole warp runs the loop with no lane-divergent code but the elected issue.
+        // This warp's chain per step (one barrier test, the MMAs, one commit, a little
+        // bookkeeping) is what paces the kernel once the rings are deep enough -- the
+        // operands of a step are ready thousands of cycles before it gets to them -- so
+        // it carries nothing else: one plain wait per step, no look-ahead test.
+        int sa = 0, bu = 0, nb = 0;  // step i: A slot i % SA, barriers i % NB, B units as the producer hands them out
         uint32_t ph = 0;             // (i / NB) & 1
         bool ok = true;
         int it = 0;
-        bool ready = false;  // full[nb] already seen complete for phase ph
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
             const TileInfo ti = decode_tile(tile, m_tiles, tt, E);
             const int set = it % SETS, round = it / SETS;
@@ -307,36 +341,47 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             if (!ok)
                 break;
             tc_fence_after();  // the epilogue's tcgen05.ld of this set came before
+            if (lane == 0)
+                TRACE(it * n_steps, 12);
             const uint32_t d_tmem = tmem_base + (uint32_t)(set * BN);
             const uint32_t idesc = make_idesc(ti.n_mma);
-            for (int ks = 0; ks < k_stages; ks++) {
-                if (!ready) {
-                    ok = mbar_wait(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok)
-                        break;
-                }
-                int nb_next = nb;
-                uint32_t ph_next = ph;
-                RING_ADVANCE(nb_next, ph_next, NB);
-                const uint32_t peek = mbar_try_wait(bar_full(nb_next), ph_next);
+            const int need = ti.n_mma >> 5;                    // B units per step
+            const uint32_t sub_step = (uint32_t)ti.n_mma * 8u;  // one chunk's tile in descriptor units of 16 bytes
+            for (int st = 0; st < n_steps; st++) {
+                ok = mbar_wait(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                if (lane == 0)
+                    TRACE(it * n_steps + st, 4);
                 tc_fence_after();  // the decode warps' tcgen05.st of this step came before
                 const uint32_t a_tmem = tmem_base + (uint32_t)(TMEM_A0 + sa * A_SLOT_COLS);
-                const uint64_t b_desc = make_sw128_desc(smem_u32(b_ring + sb * B_SLOT_BYTES));
+                if (need == 2 && (bu & 1))
+                    bu = (bu + 1) & (SBU - 1);
+                const uint64_t b_desc = make_sw128_desc(smem_u32(b_ring + bu * B_UNIT_BYTES));
+                const uint32_t b_lo = (uint32_t)b_desc, b_hi = (uint32_t)(b_desc >> 32);
+                const int nch = min(CS, k_stages - st * CS);
                 if (elect_one_sync()) {
+                    TRACE(it * n_steps + st, 13);
 #pragma unroll
-                    for (int kk = 0; kk < KSTAGE / 16; kk++)
-                        umma_ts_bf16(d_tmem, a_tmem + (uint32_t)(kk * 8), b_desc + (uint64_t)(kk * 2), idesc,
-                                     (ks | kk) != 0 ? 1u : 0u);
+                    for (int j = 0; j < CS; j++) {
+                        if (j < nch) {
+#pragma unroll
+                            for (int kk = 0; kk < KSTAGE / 16; kk++)
+                                umma_ts_bf16(d_tmem, a_tmem + (uint32_t)(j * A_SUB_COLS + kk * 8),
+                                             b_lo + (uint32_t)j * sub_step + (uint32_t)(kk * 2), b_hi, idesc,
+                                             (st | j | kk) != 0 ? 1u : 0u);
+                        }
+                    }
+                    TRACE(it * n_steps + st, 14);
                     umma_commit(bar_empty(nb));  // frees both slots when these MMAs have read them
                 }
-                ready = __all_sync(0xffffffffu, peek != 0);
-                nb = nb_next;
-                ph = ph_next;
+                if (lane == 0)
+                    TRACE(it * n_steps + st, 5);
+                RING_ADVANCE(nb, ph, NB);
                 if (++sa == SA)
                     sa = 0;
-                if (++sb == SB)
-                    sb = 0;
+                bu = (bu + need) & (SBU - 1);
             }
             if (ok && elect_one_sync())
                 umma_commit(bar_tmem_full(set));
@@ -354,41 +399,64 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
         const uint32_t a_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)TMEM_A0;
         const int my_tiles = (int)blockIdx.x < total_tiles
                                  ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-        const int total_steps = my_tiles * k_stages;
+        const int total_steps = my_tiles * n_steps;
         bool ok = true;
         for (int i = g; ok && i < total_steps; i += G) {
             // A slot i % SA is free when step i - SA is done: barrier (i - SA) % NB
             const int sw = i % WS, sa = i % SA, nb = i % NB, eb = (i - SA + NB) % NB;
             const uint32_t phw = (uint32_t)(i / WS) & 1u, phe = (uint32_t)((i - SA) / NB) & 1u;
+            const int st = i % n_steps;  // step inside its work item
+            const int nch = min(CS, k_stages - st * CS);
             ok = mbar_wait(bar_w_full(sw), phw, status, DS_TIMEOUT_FULL_W, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
-            const unsigned char* wst = w_ring + sw * CHUNK_BYTES;
-            const uint4 q0 = *reinterpret_cast<const uint4*>(wst + r * 16);
-            const uint4 q1 = *reinterpret_cast<const uint4*>(wst + PLANE_BYTES + r * 16);
-            const uint32_t sc = *reinterpret_cast<const uint16_t*>(wst + 2 * PLANE_BYTES + r * 2);
-            const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu);
-            const uint32_t mult1 = mxfp4_scale_mult(sc >> 8);
-            const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            uint32_t d[8][4];  // d[c][p] = bf16x2 of columns 8c + 2p, 8c + 2p + 1: tensor-memory column 4c + p
+            if ((u & 127) == 0)
+                TRACE(i, 6);
+            const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
+            const uint32_t a_slot = a_lane + (uint32_t)(sa * A_SLOT_COLS);
+            for (int j = 0; j < nch; j++) {
+                const unsigned char* wc = wst + j * CHUNK_BYTES;
+                const uint4 q0 = *reinterpret_cast<const uint4*>(wc + r * 16);
+                const uint4 q1 = *reinterpret_cast<const uint4*>(wc + PLANE_BYTES + r * 16);
+                const uint32_t sc = *reinterpret_cast<const uint16_t*>(wc + 2 * PLANE_BYTES + r * 2);
+                if (j == nch - 1) {
+                    // the last packed bytes of the step are in registers: the slot can be refilled
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(bar_w_empty(sw));
+                }
+                const uint32_t mult0 = mxfp4_scale_mult(sc & 0xFFu);
+                const uint32_t mult1 = mxfp4_scale_mult(sc >> 8);
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                uint32_t d[8][4];  // d[c][p] = bf16x2 of columns 8c + 2p, 8c + 2p + 1: tensor-memory column 4c + p
 #pragma unroll
-            for (int c = 0; c < 8; c++)
-                mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d[c]);
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(bar_w_empty(sw));
-            if (i >= SA)
-                ok = mbar_wait(bar_empty(eb), phe, status, DS_TIMEOUT_EMPTY, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
+                for (int c = 0; c < 8; c++)
+                    mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d[c]);
+                if (j == 0) {
+                    // the first chunk is decoded before the wait for the A slot, so that the
+                    // ALU work overlaps the MMAs still reading it
+                    if ((u & 127) == 0)
+                        TRACE(i, 7);
+                    if (i >= SA)
+                        ok = mbar_wait(bar_empty(eb), phe, status, DS_TIMEOUT_EMPTY, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok)
+                        break;
+                    if ((u & 127) == 0)
+                        TRACE(i, 8);
+                    tc_fence_after();  // the MMAs that read this slot are done (commit -> empty)
+                }
+                tmem_st_32x32(a_slot + (uint32_t)(j * A_SUB_COLS), &d[0][0]);
+            }
             if (!ok)
                 break;
-            tc_fence_after();  // the MMAs that read this slot are done (commit -> empty)
-            tmem_st_32x32(a_lane + (uint32_t)(sa * A_SLOT_COLS), &d[0][0]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(bar_full(nb));
+            if ((u & 127) == 0)
+                TRACE(i, 9);
         }
     } else {
         // ------------------------------ epilogue ------------------------------
@@ -406,6 +474,8 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
+            if (warp == EPI_WARP0 && lane == 0)
+                TRACE(it * n_steps, 10);
             tc_fence_after();
             const int mt = ti.mt;
             const float* be = bias + (size_t)ti.e * bias_stride;
@@ -492,6 +562,8 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(bar_tmem_empty(set));
+            if (warp == EPI_WARP0 && lane == 0)
+                TRACE(it * n_steps, 11);
         }
         if (MODE == 1 && pio.ticket)
             __threadfence_system();  // this thread's peer stores, before the CTA is counted below

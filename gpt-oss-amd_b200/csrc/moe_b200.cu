@@ -19,7 +19,6 @@
 #include "gemm_mma.cuh"
 #endif
 #include "gemm_tc5_pair.cuh"
-#include "gemm_tc5_swap.cuh"
 #include "gemm_tc5_ts.cuh"
 #include "mxfp4.cuh"
 #include "plan.cuh"
@@ -92,7 +91,6 @@ struct moe_b200_handle_s {
 
     tc5::TensorMaps maps_x{}, maps_h{};  // TMA maps over the GEMM inputs
     int pair_grid = 0;       // CTAs of the pair GEMM (2 x resident clusters)
-    bool small_gemm_ts = true;  // small batches: decoded weights in tensor memory (else in shared memory)
     int smem_attr_done = 0;  // bit set: shared-memory opt-in of a kernel family done on this device
 
     ep::State ep;
@@ -177,6 +175,19 @@ moe_b200_status make_maps(moe_b200_handle h, tc5::TensorMaps* maps, void* base, 
             return fail(h, MOE_B200_ERR_CUDA,
                         "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     }
+    for (int i = 0; i < 2; i++) {
+        // [chunk][row][64 columns]: the chunk axis has the smallest stride (128 bytes)
+        cuuint64_t dims[3] = {(cuuint64_t)KSTAGE, (cuuint64_t)rows, (cuuint64_t)(cols / KSTAGE)};
+        cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)KSTAGE * 2};
+        cuuint32_t box[3] = {(cuuint32_t)KSTAGE, (cuuint32_t)(32 << i), (cuuint32_t)tc5::STEP_CHUNKS};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = encode(&maps->box3[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides,
+                            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(h, MOE_B200_ERR_CUDA,
+                        "cuTensorMapEncodeTiled (3-d) failed with code " + std::to_string((int)r));
+    }
     return MOE_B200_OK;
 }
 
@@ -189,7 +200,7 @@ moe_b200_status check_layer(moe_b200_handle h, int layer) {
 }
 
 constexpr int TC5_BN = 256;                   // token rows per tile of the large-batch GEMM
-constexpr int SWAP_MAX_ROWS_PER_EXPERT = 96;  // at most this many rows per expert: small-batch GEMM
+constexpr int SMALL_MAX_ROWS_PER_EXPERT = 64; // at most this many rows per expert on average: small-batch GEMM
 
 // Token rows per routing block (16 x the router kernel's MT): a block streams the whole
 // router matrix from L2 whatever its height, so large batches use tall blocks and small
@@ -355,34 +366,6 @@ moe_b200_status launch_pair(moe_b200_handle h, const LayerWeights& lw, const tc5
     return MOE_B200_OK;
 }
 
-// Small batches: token rows on the TMEM lanes, 256 weight rows per tile (gemm_tc5_swap.cuh).
-moe_b200_status launch_swap(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
-                            const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
-                            const int* row_dst, const peer::GemmPeerIO& pio, cudaStream_t st) {
-    const moe_b200_config& c = h->cfg;
-    const int H = c.hidden_dim, I = c.intermediate_dim, EL = h->n_local;
-    namespace sw = tc5::swp;
-    if (!(h->smem_attr_done & 2)) {
-        CU_TRY(h, cudaFuncSetAttribute(sw::expert_gemm_swap_kernel<0>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, sw::SMEM_BYTES));
-        CU_TRY(h, cudaFuncSetAttribute(sw::expert_gemm_swap_kernel<1>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, sw::SMEM_BYTES));
-        h->smem_attr_done |= 2;
-    }
-    prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
-    sw::expert_gemm_swap_kernel<0><<<h->n_sms, sw::N_THREADS, sw::SMEM_BYTES, st>>>(
-        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-        EL, h->hbuf, I, I, nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
-    prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
-    prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
-    sw::expert_gemm_swap_kernel<1><<<h->n_sms, sw::N_THREADS, sw::SMEM_BYTES, st>>>(
-        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
-        EL, yout, H, H, row_dst, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
-    prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
-    h->last_launches += 2;
-    return MOE_B200_OK;
-}
-
 // Small batches, decoded weights in tensor memory (gemm_tc5_ts.cuh).
 moe_b200_status launch_ts(moe_b200_handle h, const LayerWeights& lw, const tc5::TensorMaps& maps_x,
                           const int* g_off, const int* g_cnt, const int* g_tile_start, float* yout,
@@ -447,12 +430,8 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
     (void)H;
     (void)I;
     (void)EL;
-    if (bn == tc5::swp::BM) {
-        static_assert(tc5::swp::BM == tc5::ts::BN, "both small-batch kernels use tables of 128-row tiles");
-        if (h->small_gemm_ts)
-            return launch_ts(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
-        return launch_swap(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
-    }
+    if (bn == tc5::ts::BN)
+        return launch_ts(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
     if (bn == TC5_BN)
         return launch_pair(h, lw, maps_x, g_off, g_cnt, g_tile_start, yout, row_dst, pio, st);
     return fail(h, MOE_B200_ERR_INVALID, "tile tables were built for another tile height");
@@ -467,8 +446,8 @@ int permute_split(moe_b200_handle h, int nblk, int n_assign) {
 
 // Token rows per GEMM tile for a call that has `rows` rows spread over the local
 // experts; the tile tables are built for it and it selects the kernel: few rows per
-// expert (bound by weight streaming and by the MMA warp's per-step chain) -> token
-// rows on the TMEM lanes, 128 per tile; otherwise weights on the lanes and 256
+// expert (bound by streaming the weights) -> the single-CTA kernel with the decoded
+// weights in tensor memory, 64 token rows per tile; otherwise CTA pairs and 256
 // token rows per tile.  Any choice is correct for any distribution of rows.
 int pick_bn(moe_b200_handle h, int rows) {
 #ifdef MOE_B200_TEST_AIDS
@@ -476,7 +455,7 @@ int pick_bn(moe_b200_handle h, int rows) {
         return V0_BN;
 #endif
     const int per_expert = rows / (h->n_local > 0 ? h->n_local : 1);
-    return per_expert <= SWAP_MAX_ROWS_PER_EXPERT ? tc5::swp::BM : TC5_BN;
+    return per_expert <= SMALL_MAX_ROWS_PER_EXPERT ? tc5::ts::BN : TC5_BN;
 }
 
 moe_b200_status check_shard(moe_b200_handle h, int first_expert, int n) {
@@ -621,8 +600,6 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
         return fail(nullptr, MOE_B200_ERR_INVALID, "out of host memory");
     h->cfg = c;
     h->n_sms = prop.multiProcessorCount;
-    if (const char* v = getenv("MOE_B200_SMALL_GEMM"))
-        h->small_gemm_ts = strcmp(v, "swap") != 0;
     moe_b200_shard_range(c.n_experts, c.ep_size, c.ep_rank, &h->first_expert, &h->n_local);
     const int H = c.hidden_dim, I = c.intermediate_dim, E = c.n_experts, K = c.experts_per_token;
     h->m_tiles1 = ceil_div(2 * I, TILE_M);

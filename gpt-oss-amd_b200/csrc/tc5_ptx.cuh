@@ -1,4 +1,4 @@
-// PTX wrappers shared by the tcgen05 expert GEMMs (gemm_tc5_pair.cuh, gemm_tc5_swap.cuh):
+// PTX wrappers shared by the tcgen05 expert GEMMs (gemm_tc5_pair.cuh, gemm_tc5_ts.cuh):
 // mbarrier, TMA / bulk copies, tensor-memory allocation, tcgen05.mma / commit / ld,
 // shared-memory and instruction descriptors, bounded waits.
 #pragma once
@@ -10,9 +10,15 @@ namespace moe {
 namespace tc5 {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr uint32_t WAIT_SUSPEND_NS = 20000;                 // one suspended test of a barrier lasts at most this
+
+constexpr int STEP_CHUNKS = 3;  // 64-column chunks per pipeline step of the small-batch GEMM
 
 struct TensorMaps {
-    CUtensorMap box[4];  // token-row boxes of 32, 64, 128 (and 256, unused) rows x 64 columns
+    CUtensorMap box[4];   // token-row boxes of 32, 64, 128 (and 256, unused) rows x 64 columns
+    // the same rows seen as [chunk of 64 columns][row][64 columns]: boxes of 32 and 64 rows x
+    // STEP_CHUNKS chunks, so that one copy brings the activation tiles of a whole step
+    CUtensorMap box3[2];
 };
 
 // ---------------------------------------------------------------------------
@@ -47,6 +53,23 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return done;
 }
 
+// The same test, but the thread may stay suspended in hardware for up to `ns`
+// nanoseconds waiting for the phase to complete (it resumes at once when it does).
+// A role that waits in a loop of plain tests takes issue slots from the warps that
+// have work -- above all from the single warp that issues the MMAs, whose chain of a
+// few dozen instructions per step then sets the pace of the whole pipeline.
+__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return done;
+}
+
 // One lane of a converged warp (the same one every time).
 __device__ __forceinline__ uint32_t elect_one_sync() {
     uint32_t pred;
@@ -72,9 +95,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
         return true;
     unsigned long long t_start = 0;
     for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity))
+        if (mbar_try_wait_suspend(bar, parity, WAIT_SUSPEND_NS))
             return true;
-        if ((it & 127u) == 0) {
+        if ((it & 15u) == 0) {
             if (*abort_flag)
                 return false;
             const unsigned long long now = global_timer_ns();
@@ -124,6 +147,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
 

@@ -21,6 +21,9 @@ max-abs is always reported beside the adjusted one and has its own ceiling,
 ``RAW_MAX_ABS_CEILING`` = 0.1, about what ONE flip of the largest h can do at the
 benchmark's value distributions (0.25 * 0.375 * w with w < 1; measured raw
 figures: 0.01 - 0.05), so that a real error cannot hide behind the accounting.
+Where the GPU's h cannot be read back (expert-parallel runs: the rows of a token
+are computed on other GPUs) no flip can be identified, ``max_abs_adjusted`` is
+None and the max-abs gate is the raw ceiling alone, next to the rel-L2 gate.
 """
 from __future__ import annotations
 
@@ -64,7 +67,7 @@ def measure(res, ref, top_k):
          "err_sq": float((err ** 2).sum()), "ref_sq": float((b ** 2).sum()),
          "max_abs_raw": float(np.abs(err).max(initial=0.0)), "h_flips": 0, "h_elements": 0,
          "h_more_than_one_ulp": 0}
-    m["max_abs_adjusted"] = m["max_abs_raw"]
+    m["max_abs_adjusted"] = m["max_abs_raw"] if "h_bits" in res else None
     if mism == 0 and "h_bits" in res and "h" in ref:
         h_gpu = bf16_bits_to_f32(res["h_bits"])[ok].astype(np.float64)
         h_ref = ref["h"][ok].astype(np.float64)
@@ -98,8 +101,12 @@ def merge(parts):
         for k in ("tokens", "ties_excluded", "topk_mismatches", "err_sq", "ref_sq", "h_flips",
                   "h_elements", "h_more_than_one_ulp"):
             out[k] += m[k]
-        for k in ("topk_w_err", "max_abs_raw", "max_abs_adjusted"):
+        for k in ("topk_w_err", "max_abs_raw"):
             out[k] = max(out[k], m[k]) if not (np.isnan(m[k]) or np.isnan(out[k])) else float("nan")
+        if m["max_abs_adjusted"] is None or out["max_abs_adjusted"] is None:
+            out["max_abs_adjusted"] = None  # one part without the intermediate: no adjusted figure
+        else:
+            out["max_abs_adjusted"] = max(out["max_abs_adjusted"], m["max_abs_adjusted"])
         out["finite"] = out["finite"] and m["finite"]
     return out
 
@@ -122,11 +129,14 @@ def finish(m):
             why.append(f"{m['h_more_than_one_ulp']} intermediates differ by more than one bf16 ulp")
         if m["h_elements"] and m["h_flips"] / m["h_elements"] > FLIP_RATE_TOL:
             why.append(f"flip rate {m['h_flips'] / m['h_elements']:.2e} > {FLIP_RATE_TOL}")
-        if m["max_abs_adjusted"] > MAX_ABS_TOL:
+        if m["max_abs_adjusted"] is not None and m["max_abs_adjusted"] > MAX_ABS_TOL:
             why.append(f"max-abs {m['max_abs_adjusted']:.3e} > {MAX_ABS_TOL} (raw {m['max_abs_raw']:.3e}, "
                        f"{m['h_flips']} h flips)")
         if m["max_abs_raw"] > RAW_MAX_ABS_CEILING:
             why.append(f"raw max-abs {m['max_abs_raw']:.3e} > ceiling {RAW_MAX_ABS_CEILING}")
+    m["max_abs_gate"] = (f"adjusted <= {MAX_ABS_TOL}, raw <= {RAW_MAX_ABS_CEILING}"
+                         if m["max_abs_adjusted"] is not None else
+                         f"raw <= {RAW_MAX_ABS_CEILING} (intermediate not readable: no flip accounting)")
     m["ok"] = not why
     m["why"] = "; ".join(why)
     for k in ("err_sq", "ref_sq"):
