@@ -26,21 +26,20 @@
 // carries only the packed bytes and the small activation tile.
 //
 // One persistent CTA per SM walks work items (expert, 128-row weight tile, tile
-// of up to 64 token rows).  A pipeline STEP covers CS = 3 chunks of 64 K-columns
-// (192 columns, 13 KB of packed weights: one bulk copy, the chunks of a weight
-// tile are contiguous): every hand-off between the roles -- a barrier wait, an
-// arrival, a commit -- costs a few hundred cycles whatever it carries, and with one
-// chunk per step the MMA-issuing warp's wait / issue / commit chain alone held the
-// kernel at a third of the HBM rate (measured: removing the decode arithmetic, the
-// tensor-memory stores and three of the four MMAs changed the time by 15 %).  Rings:
+// of up to 64 token rows).  A pipeline STEP covers CS = 6 chunks of 64 K-columns
+// (384 columns, 26 KB of packed weights: one bulk copy, the chunks of a weight
+// tile are contiguous).  Two measurements set that size.  (1) Bulk copies of one
+// chunk (4352 B) stream at 2.6 TB/s over the whole GPU however deep the ring is,
+// copies of three chunks or more at 6.1 TB/s: a copy has a fixed cost.  (2) The
+// MMA-issuing warp needs ~25 cycles per tcgen05.mma at N = 32 (the tensor pipe's
+// own rate) but ~800 cycles per step around them -- one barrier test, one commit
+// and a little bookkeeping, each a round trip through a memory pipe that sixteen
+// decode warps keep busy -- and it is the only warp that can issue them.  Rings:
 //   W ring   packed MXFP4 steps in shared memory (bulk copies; covers HBM latency)
-//   A ring   SA slots of 96 tensor-memory columns (decoded weights)
-//   B ring   activation tiles in shared memory (TMA, no multicast), handed out in
-//            units of 12 KB: a step of an item with up to 32 token rows takes one
-//            unit, with up to 64 rows two.  A TMA load takes ~2000 cycles to land, so
-//            what matters is how many steps are in flight: eight for the usual
-//            decode-shaped item (with four the kernel waited for activations, not
-//            for weights)
+//   A ring   SA = 2 slots of 192 tensor-memory columns (decoded weights)
+//   B ring   activation tiles in shared memory (one 3-d TMA box per step, no
+//            multicast), handed out in units of 24 KB: a step of an item with up to
+//            32 token rows takes one unit, with up to 64 rows two
 // and NB barrier pairs indexed by the step number: full[i % NB] collects the
 // decode warps' arrivals and the TMA bytes of step i, empty[i % NB] is signalled
 // by tcgen05.commit when the MMAs of step i are done.
@@ -48,8 +47,10 @@
 // Warp roles:
 //   warp 0      W producer          warp 1   B producer (TMA)
 //   warp 2      allocates tensor memory, issues tcgen05.mma, commits
-//   next 16     decode packed MXFP4 -> bf16 -> tensor memory: four groups of four
-//               warps, group g decodes steps g, g + 4, ...; a thread owns one row
+//   next 16     decode packed MXFP4 -> bf16 -> tensor memory: two groups of eight
+//               warps, group g decodes steps g, g + 2, ...; two warps share a
+//               quarter of the rows, one takes the even chunks of the step, the
+//               other the odd ones, so that a slot is refilled in half the time
 //   last 4      epilogue: tcgen05.ld, bias, SwiGLU / store
 //
 // Every mbarrier wait is bounded in time; a wait that runs out records a code in
@@ -66,24 +67,25 @@ namespace ts {
 constexpr int BN = 64;                       // most token rows per work item (UMMA N)
 constexpr int CS = STEP_CHUNKS;              // chunks of 64 K-columns per pipeline step
 constexpr int B_UNIT_BYTES = CS * 32 * 128;  // activation tiles of one step for 32 token rows (32 rows x 64 bf16 per chunk, SW128)
-constexpr int SBU = 8;                       // units in the B ring
+constexpr int SBU = 4;                       // units in the B ring
 constexpr int W_SLOT_BYTES = CS * CHUNK_BYTES;
 constexpr int A_SUB_COLS = KSTAGE / 2;       // one decoded chunk in tensor memory: 128 lanes x 32 columns of bf16x2
 constexpr int A_SLOT_COLS = CS * A_SUB_COLS;
 constexpr int MMA_WARP = 2;
 constexpr int DEQ_WARP0 = 3;
-constexpr int G = 4;                         // decode groups of four warps
+constexpr int G = 2;                         // decode groups
+constexpr int GW = 8;                        // warps per decode group: two per quarter of the rows
 //   SA  A slots (tensor memory)   SB  activation slots   WS  packed slots   NB  barrier pairs
 // SA and WS are multiples of G, so the successive fills of a slot are handled by one
 // group in program order (an mbarrier parity wait cannot tell phase n from phase n-2).
-constexpr int SA = 4, NB = 8, WS = 8;
+constexpr int SA = 2, NB = 4, WS = 4;
 constexpr int SETS = 2;                      // accumulator sets: the MMAs of item i+1 overlap the epilogue of item i
 constexpr int TMEM_A0 = SETS * BN;           // first tensor-memory column of the A slots
 constexpr int TMEM_COLS = 512;
 static_assert(TMEM_A0 + SA * A_SLOT_COLS <= TMEM_COLS, "tensor memory");
 static_assert(SA % G == 0 && WS % G == 0 && NB % SA == 0 && NB % G == 0 && NB >= SBU,
               "a slot's successive fills must belong to one decode group");
-constexpr int EPI_WARP0 = DEQ_WARP0 + 4 * G;
+constexpr int EPI_WARP0 = DEQ_WARP0 + GW * G;
 constexpr int N_THREADS = (EPI_WARP0 + 4) * 32;  // 736
 constexpr int MAX_LOCAL_EXPERTS = 256;
 constexpr int EPI_STAGE_BYTES = 2048;
@@ -195,10 +197,10 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
     if (threadIdx.x == 0) {
         for (int s = 0; s < WS; s++) {
             mbar_init(bar_w_full(s), 1);
-            mbar_init(bar_w_empty(s), 4);  // one elected arrival per warp of the decoding group
+            mbar_init(bar_w_empty(s), GW);  // one elected arrival per warp of the decoding group
         }
         for (int s = 0; s < NB; s++) {
-            mbar_init(bar_full(s), 4 + 1);  // four decode warps + the TMA producer's expect_tx
+            mbar_init(bar_full(s), GW + 1);  // the decode warps of a group + the TMA producer's expect_tx
             mbar_init(bar_empty(s), 1);     // tcgen05.commit
         }
         for (int b = 0; b < SETS; b++) {
@@ -394,7 +396,8 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
         // Packed chunk -> registers (before the wait for the A slot, so that the ALU
         // work overlaps the MMAs still reading it) -> tcgen05.st.
         const int u = threadIdx.x - DEQ_WARP0 * 32;
-        const int g = u >> 7;
+        const int g = u / (GW * 32);
+        const int half = ((u >> 5) % GW) >> 2;  // 0: this warp takes chunks 0, 2, 4 of a step; 1: chunks 1, 3, 5
         const int r = (warp & 3) * 32 + lane;
         const uint32_t a_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)TMEM_A0;
         const int my_tiles = (int)blockIdx.x < total_tiles
@@ -411,17 +414,18 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
-            if ((u & 127) == 0)
+            if ((u & (GW * 32 - 1)) == 0)
                 TRACE(i, 6);
             const unsigned char* wst = w_ring + sw * W_SLOT_BYTES;
             const uint32_t a_slot = a_lane + (uint32_t)(sa * A_SLOT_COLS);
-            for (int j = 0; j < nch; j++) {
+            bool slot_free = false;
+            for (int j = half; j < nch; j += 2) {
                 const unsigned char* wc = wst + j * CHUNK_BYTES;
                 const uint4 q0 = *reinterpret_cast<const uint4*>(wc + r * 16);
                 const uint4 q1 = *reinterpret_cast<const uint4*>(wc + PLANE_BYTES + r * 16);
                 const uint32_t sc = *reinterpret_cast<const uint16_t*>(wc + 2 * PLANE_BYTES + r * 2);
-                if (j == nch - 1) {
-                    // the last packed bytes of the step are in registers: the slot can be refilled
+                if (j + 2 >= nch) {
+                    // this warp's last packed bytes of the step are in registers
                     __syncwarp();
                     if (lane == 0)
                         mbar_arrive(bar_w_empty(sw));
@@ -433,29 +437,43 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
 #pragma unroll
                 for (int c = 0; c < 8; c++)
                     mxfp4_decode_word(w[c], c < 4 ? mult0 : mult1, d[c]);
-                if (j == 0) {
+                if (!slot_free) {
                     // the first chunk is decoded before the wait for the A slot, so that the
                     // ALU work overlaps the MMAs still reading it
-                    if ((u & 127) == 0)
+                    if ((u & (GW * 32 - 1)) == 0)
                         TRACE(i, 7);
                     if (i >= SA)
                         ok = mbar_wait(bar_empty(eb), phe, status, DS_TIMEOUT_EMPTY, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok)
                         break;
-                    if ((u & 127) == 0)
+                    if ((u & (GW * 32 - 1)) == 0)
                         TRACE(i, 8);
                     tc_fence_after();  // the MMAs that read this slot are done (commit -> empty)
+                    slot_free = true;
                 }
                 tmem_st_32x32(a_slot + (uint32_t)(j * A_SUB_COLS), &d[0][0]);
             }
             if (!ok)
                 break;
+            if (half >= nch) {
+                // a step with a single chunk leaves the odd-chunk warps without work: they
+                // still release the packed slot and still wait for step i - SA, so that no
+                // warp ever arrives twice within one phase of a barrier
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(bar_w_empty(sw));
+                if (i >= SA)
+                    ok = mbar_wait(bar_empty(eb), phe, status, DS_TIMEOUT_EMPTY, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(bar_full(nb));
-            if ((u & 127) == 0)
+            if ((u & (GW * 32 - 1)) == 0)
                 TRACE(i, 9);
         }
     } else {

@@ -12,7 +12,7 @@ namespace tc5 {
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 constexpr uint32_t WAIT_SUSPEND_NS = 20000;                 // one suspended test of a barrier lasts at most this
 
-constexpr int STEP_CHUNKS = 3;  // 64-column chunks per pipeline step of the small-batch GEMM
+constexpr int STEP_CHUNKS = 6;  // 64-column chunks per pipeline step of the small-batch GEMM
 
 struct TensorMaps {
     CUtensorMap box[4];   // token-row boxes of 32, 64, 128 (and 256, unused) rows x 64 columns
