@@ -143,9 +143,20 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int m_pairs, const Til
     const int ntl = tt.tile_start[lo + 1] - tt.tile_start[lo];
     const int r = tile - tt.tile_start[lo] * m_pairs;
     ti.mp = r / ntl;
-    const int n0 = (r - ti.mp * ntl) * BN;
+    // The expert's rows are cut into ntl = ceil(cnt / BN) items of EQUAL size (rounded up
+    // to the MMA's granule) instead of full items plus a remainder: every item costs a
+    // full pass of weight decoding whatever its rows, so three items of 176 rows finish
+    // sooner than 256 + 256 + 16 (the decode of a step hides behind a shorter MMA).
+    const int cnt = tt.cnt[lo];
+    int rows = BN;
+    if (ntl > 1) {
+        const int q = ((cnt + ntl - 1) / ntl + 31) & ~31;
+        if (q < BN && (ntl - 1) * q < cnt)
+            rows = q;
+    }
+    const int n0 = (r - ti.mp * ntl) * rows;
     ti.row0 = tt.off[lo] + n0;
-    ti.valid_n = min(BN, tt.cnt[lo] - n0);
+    ti.valid_n = min(rows, cnt - n0);
     ti.n_mma = max(32, (ti.valid_n + 31) & ~31);
     const int nh = ti.n_mma >> 1;
     ti.box_idx = nh <= 32 ? 0 : nh <= 64 ? 1 : 2;
