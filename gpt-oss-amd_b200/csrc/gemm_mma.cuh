@@ -45,7 +45,7 @@ __device__ __forceinline__ int find_expert(const int* __restrict__ tile_start, i
 template <int MODE>
 __global__ void __launch_bounds__(256)
 expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride, int k_stages,
-                       const float* __restrict__ bias, int bias_stride,
+                       const float* __restrict__ bias, const float* __restrict__ rscale, int bias_stride,
                        const uint16_t* __restrict__ xin, int K, const int* __restrict__ g_off,
                        const int* __restrict__ g_cnt, const int* __restrict__ g_tile_start, int E,
                        void* __restrict__ outp, int out_ld, int out_rows_valid,
@@ -131,6 +131,7 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
     }
 
     const float* be = bias + (size_t)e * bias_stride;
+    const float* rse = rscale + (size_t)e * bias_stride;
     if (MODE == 0) {
         // acc[0] = gate rows, acc[1] = matching up rows (smem rows p and 64+p)
         uint16_t* h = static_cast<uint16_t*>(outp);
@@ -141,14 +142,15 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
             if (j >= out_rows_valid)
                 continue;
             const float bg = be[mt * TILE_M + 2 * p], bu = be[mt * TILE_M + 2 * p + 1];
+            const float sg = rse[mt * TILE_M + 2 * p], su = rse[mt * TILE_M + 2 * p + 1];
 #pragma unroll
             for (int nb = 0; nb < 4; nb++)
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
                     const int col = nh * 32 + nb * 8 + 2 * t + c;
                     if (col < valid_n) {
-                        const float v = swiglu(acc[0][nb][2 * half + c] + bg,
-                                               acc[1][nb][2 * half + c] + bu, alpha, limit);
+                        const float v = swiglu(fmaf(acc[0][nb][2 * half + c], sg, bg),
+                                               fmaf(acc[1][nb][2 * half + c], su, bu), alpha, limit);
                         h[(size_t)(row0 + col) * out_ld + j] = (uint16_t)float_to_bf16_bits(v);
                     }
                 }
@@ -162,7 +164,7 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
                 const int m = mt * TILE_M + (pi + 4 * a) * 16 + g + 8 * half;
                 if (m >= out_rows_valid)
                     continue;
-                const float bm = be[m];
+                const float bm = be[m], rs = rse[m];
 #pragma unroll
                 for (int nb = 0; nb < 4; nb++)
 #pragma unroll
@@ -170,7 +172,7 @@ expert_gemm_mma_kernel(const uint8_t* __restrict__ chunks, size_t expert_stride,
                         const int col = nh * 32 + nb * 8 + 2 * t + c;
                         if (col < valid_n) {
                             float* yrow = y + (size_t)(row_dst ? row_dst[row0 + col] : (row0 + col)) * out_ld;
-                            yrow[m] = acc[a][nb][2 * half + c] + bm;
+                            yrow[m] = fmaf(acc[a][nb][2 * half + c], rs, bm);
                         }
                     }
             }

@@ -166,7 +166,8 @@ template <int MODE>
 __global__ void __launch_bounds__(N_THREADS, 1)
 expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __restrict__ chunks,
                       size_t expert_stride, int k_stages, int m_tiles,
-                      const float* __restrict__ bias, int bias_stride,
+                      const float* __restrict__ bias, const float* __restrict__ rscale,
+                        int bias_stride,
                       const int* __restrict__ g_off, const int* __restrict__ g_cnt,
                       const int* __restrict__ g_tile_start, int E, void* __restrict__ outp,
                       int out_ld, int out_rows_valid, const int* __restrict__ row_dst,
@@ -497,6 +498,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             tc_fence_after();
             const int mt = ti.mt;
             const float* be = bias + (size_t)ti.e * bias_stride;
+                const float* rse = rscale + (size_t)ti.e * bias_stride;  // 2^shift of every weight row
             const int m = mt * TILE_M + row;
             const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(set * BN);
             if (MODE == 0) {
@@ -507,7 +509,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
                 // store writes 16 bytes per lane.
                 uint16_t* h = static_cast<uint16_t*>(outp);
                 uint16_t* stage16 = reinterpret_cast<uint16_t*>(stage);
-                const float bm = be[m];  // 2I is a multiple of TILE_M: always in range
+                const float bm = be[m], rs = rse[m];  // 2I is a multiple of TILE_M: always in range
                 const int jf0 = (mt * TILE_M + q * 32) >> 1;  // first of this warp's 16 features
                 const bool odd = (lane & 1) != 0;
                 // token rows 16..31 sit 64 bytes further: no bank conflict between the halves
@@ -517,7 +519,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
                     tmem_ld_sum<1, BN>(t_addr + (uint32_t)c0, v);
 #pragma unroll
                     for (int c = 0; c < 16; c++) {
-                        const float mine_lo = v[c] + bm, mine_hi = v[c + 16] + bm;
+                        const float mine_lo = fmaf(v[c], rs, bm), mine_hi = fmaf(v[c + 16], rs, bm);
                         const float send = odd ? mine_lo : mine_hi;
                         const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
                         const float gate = odd ? recv : mine_lo;
@@ -542,6 +544,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
                 float* y = static_cast<float*>(outp);
                 float* stage32 = reinterpret_cast<float*>(stage);
                 const float bm = (m < out_rows_valid) ? be[m] : 0.f;
+                    const float rs = (m < out_rows_valid) ? rse[m] : 1.f;
                 const int m4 = mt * TILE_M + q * 32 + (lane & 7) * 4;  // columns this lane stores
                 const bool m4_ok = m4 < out_rows_valid;                // the width is a multiple of 4
                 for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
@@ -551,7 +554,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
                     for (int half = 0; half < 2; half++) {
 #pragma unroll
                         for (int c = 0; c < 16; c++)
-                            stage32[c * 32 + lane] = v[half * 16 + c] + bm;
+                            stage32[c * 32 + lane] = fmaf(v[half * 16 + c], rs, bm);
                         __syncwarp();
 #pragma unroll
                         for (int p = 0; p < 4; p++) {

@@ -37,6 +37,8 @@ struct LayerWeights {
     uint8_t* w2 = nullptr;         // [n_local][m_tiles2][ks2][CHUNK_BYTES]
     float* bias1 = nullptr;        // [n_local, 2I]
     float* bias2 = nullptr;        // [n_local, H]
+    float* rscale1 = nullptr;      // [n_local, 2I]  2^shift of every gate/up weight row (mxfp4_row_shift_kernel)
+    float* rscale2 = nullptr;      // [n_local, H]
     bool router_set = false;
     std::vector<char> expert_set;
 };
@@ -88,6 +90,7 @@ struct moe_b200_handle_s {
     // upload staging (one expert matrix)
     uint8_t* stage_blocks = nullptr;
     uint8_t* stage_scales = nullptr;
+    int* stage_shift = nullptr;  // exponent shift of every row of the matrix being re-tiled
 
     tc5::TensorMaps maps_x{}, maps_h{};  // TMA maps over the GEMM inputs
     int pair_grid = 0;       // CTAs of the pair GEMM (2 x resident clusters)
@@ -296,7 +299,8 @@ cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
 template <int MODE>
 moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
                                    const tc5::TensorMaps& maps, const uint8_t* chunks, size_t stride,
-                                   int ks, int m_tiles, const float* bias, int bias_stride,
+                                   int ks, int m_tiles, const float* bias, const float* rscale,
+                                   int bias_stride,
                                    const int* g_off, const int* g_cnt, const int* g_tile_start, int EL,
                                    void* out, int out_ld, int out_valid, const int* row_dst,
                                    const peer::GemmPeerIO& pio) {
@@ -314,7 +318,8 @@ moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     CU_TRY(h, cudaLaunchKernelEx(&cfg, pr::expert_gemm_pair_kernel<MODE>, maps, chunks, stride, ks, m_tiles,
-                                 bias, bias_stride, g_off, g_cnt, g_tile_start, EL, out, out_ld, out_valid,
+                                 bias, rscale, bias_stride, g_off, g_cnt, g_tile_start, EL, out, out_ld,
+                                 out_valid,
                                  row_dst, pio, h->cfg.swiglu_alpha, h->cfg.swiglu_limit, h->status));
     return MOE_B200_OK;
 }
@@ -351,14 +356,15 @@ moe_b200_status launch_pair(moe_b200_handle h, const LayerWeights& lw, const tc5
     }
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
     moe_b200_status s1 = launch_pair_kernel<0>(h, h->pair_grid, st, maps_x, lw.w1, h->stride1, h->ks1,
-                                               h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-                                               EL, h->hbuf, I, I, nullptr, pio);
+                                               h->m_tiles1, lw.bias1, lw.rscale1, 2 * I, g_off, g_cnt,
+                                               g_tile_start, EL, h->hbuf, I, I, nullptr, pio);
     if (s1)
         return s1;
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
     s1 = launch_pair_kernel<1>(h, h->pair_grid, st, h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2,
-                               lw.bias2, H, g_off, g_cnt, g_tile_start, EL, yout, H, H, row_dst, pio);
+                               lw.bias2, lw.rscale2, H, g_off, g_cnt, g_tile_start, EL, yout, H, H, row_dst,
+                               pio);
     if (s1)
         return s1;
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
@@ -382,13 +388,13 @@ moe_b200_status launch_ts(moe_b200_handle h, const LayerWeights& lw, const tc5::
     }
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
     ts::expert_gemm_ts_kernel<0><<<h->n_sms, ts::N_THREADS, ts::SMEM_BYTES, st>>>(
-        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, 2 * I, g_off, g_cnt, g_tile_start,
-        EL, h->hbuf, I, I, nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
+        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, lw.rscale1, 2 * I, g_off, g_cnt,
+        g_tile_start, EL, h->hbuf, I, I, nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
     ts::expert_gemm_ts_kernel<1><<<h->n_sms, ts::N_THREADS, ts::SMEM_BYTES, st>>>(
-        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, H, g_off, g_cnt, g_tile_start,
-        EL, yout, H, H, row_dst, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
+        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, lw.rscale2, H, g_off, g_cnt,
+        g_tile_start, EL, yout, H, H, row_dst, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
     h->last_launches += 2;
     return MOE_B200_OK;
@@ -412,12 +418,14 @@ moe_b200_status launch_gemms(moe_b200_handle h, const LayerWeights& lw, const ui
         const int n_tiles_upper = rows_upper / V0_BN + EL;
         dim3 g1(n_tiles_upper, h->m_tiles1), g2(n_tiles_upper, h->m_tiles2);
         prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
-        expert_gemm_mma_kernel<0><<<g1, 256, 0, st>>>(lw.w1, h->stride1, h->ks1, lw.bias1, 2 * I, xin,
+        expert_gemm_mma_kernel<0><<<g1, 256, 0, st>>>(lw.w1, h->stride1, h->ks1, lw.bias1, lw.rscale1, 2 * I,
+                                                      xin,
                                                       H, g_off, g_cnt, g_tile_start, EL, h->hbuf, I,
                                                       I, nullptr, c.swiglu_alpha, c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
         prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
-        expert_gemm_mma_kernel<1><<<g2, 256, 0, st>>>(lw.w2, h->stride2, h->ks2, lw.bias2, H, h->hbuf,
+        expert_gemm_mma_kernel<1><<<g2, 256, 0, st>>>(lw.w2, h->stride2, h->ks2, lw.bias2, lw.rscale2, H,
+                                                      h->hbuf,
                                                       I, g_off, g_cnt, g_tile_start, EL, yout, H, H,
                                                       row_dst, c.swiglu_alpha, c.swiglu_limit);
         prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
@@ -470,7 +478,7 @@ moe_b200_status check_shard(moe_b200_handle h, int first_expert, int n) {
 
 // Upload of packed experts: everything is queued on one stream (copy -> re-tile ->
 // next copy into the same staging buffer are ordered by it) and the host waits once,
-// in upload_finish.  Scale bytes the one-multiply decode cannot represent are
+// in upload_finish.  Rows whose scale bytes the shifted one-multiply decode cannot hold are
 // reported through a flag word of their own, so that an older wait code in the
 // status word cannot mask them.
 moe_b200_status upload_begin(moe_b200_handle h) {
@@ -493,16 +501,20 @@ moe_b200_status upload_expert(moe_b200_handle h, int layer, int le, const uint8_
         b1 = h->stage_blocks;
         s1 = h->stage_scales;
     }
-    mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(b1, s1, 2 * I, G1,
-                                                                     lw.w1 + le * h->stride1, bad_scale);
+    mxfp4_row_shift_kernel<<<(2 * I + 7) / 8, 256, 0, s>>>(b1, s1, 2 * I, G1, h->stage_shift,
+                                                           lw.rscale1 + (size_t)le * 2 * I, bad_scale);
+    mxfp4_retile_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(b1, s1, 2 * I, G1, h->stage_shift,
+                                                                     lw.w1 + le * h->stride1);
     if (!(is_device_pointer(b2) && is_device_pointer(s2))) {
         CU_TRY(h, cudaMemcpyAsync(h->stage_blocks, b2, nb2, cudaMemcpyHostToDevice, s));
         CU_TRY(h, cudaMemcpyAsync(h->stage_scales, s2, ns2, cudaMemcpyHostToDevice, s));
         b2 = h->stage_blocks;
         s2 = h->stage_scales;
     }
-    mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(b2, s2, H, G2,
-                                                                     lw.w2 + le * h->stride2, bad_scale);
+    mxfp4_row_shift_kernel<<<(H + 7) / 8, 256, 0, s>>>(b2, s2, H, G2, h->stage_shift,
+                                                       lw.rscale2 + (size_t)le * H, bad_scale);
+    mxfp4_retile_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(b2, s2, H, G2, h->stage_shift,
+                                                                     lw.w2 + le * h->stride2);
     CU_TRY(h, cudaMemcpyAsync(lw.bias1 + (size_t)le * 2 * I, c1, (size_t)2 * I * 4, cudaMemcpyDefault, s));
     CU_TRY(h, cudaMemcpyAsync(lw.bias2 + (size_t)le * H, c2, (size_t)H * 4, cudaMemcpyDefault, s));
     return MOE_B200_OK;
@@ -518,8 +530,8 @@ moe_b200_status upload_finish(moe_b200_handle h, int layer, int first_expert, in
         lw.expert_set[first_expert + i - h->first_expert] = (sw == 0);
     if (sw != 0)
         return fail(h, MOE_B200_ERR_UNSUPPORTED,
-                    "an e8m0 scale byte above 128 (block scale above 2) was found; the in-kernel "
-                    "decode covers scale bytes 0..128");
+                    "a weight row whose blocks' e8m0 scale bytes span more than 128 binades was found "
+                    "(blocks of zeros do not count); one row of the in-kernel decode covers 128");
     return MOE_B200_OK;
 }
 
@@ -635,7 +647,9 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
             (st = dev_alloc(h, &lw.w1, h->stride1 * h->n_local)) ||
             (st = dev_alloc(h, &lw.w2, h->stride2 * h->n_local)) ||
             (st = dev_alloc(h, &lw.bias1, (size_t)h->n_local * 2 * I)) ||
-            (st = dev_alloc(h, &lw.bias2, (size_t)h->n_local * H)))
+            (st = dev_alloc(h, &lw.bias2, (size_t)h->n_local * H)) ||
+            (st = dev_alloc(h, &lw.rscale1, (size_t)h->n_local * 2 * I)) ||
+            (st = dev_alloc(h, &lw.rscale2, (size_t)h->n_local * H)))
             return bail(st);
     }
     const size_t TK = (size_t)c.max_tokens * K;
@@ -655,7 +669,8 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
                                                  : (size_t)H * (I / 32) * 16)) ||
         (st = dev_alloc(h, &h->stage_scales, (size_t)2 * I * (H / 32) > (size_t)H * (I / 32)
                                                  ? (size_t)2 * I * (H / 32)
-                                                 : (size_t)H * (I / 32))))
+                                                 : (size_t)H * (I / 32))) ||
+        (st = dev_alloc(h, &h->stage_shift, (size_t)(2 * I > H ? 2 * I : H))))
         return bail(st);
     // fp32 rows of the down GEMM before the combine: only the single-GPU path keeps
     // them here (expert-parallel results go to the token owner's receive buffer)
@@ -918,16 +933,25 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
         y_for_combine = es.yrecv;
         combine_wait = peer::flag_slot(es.table.ctrl[rank], E, G, peer::FLAG_RESULTS, 0);
     } else {
-        prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
-        plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off, h->tile_start,
-                                      h->blk_base);
-        prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
-        h->last_launches++;
+        // small batches: the permute kernel plans by itself (one launch less on the
+        // latency-bound path); otherwise a one-block plan kernel runs first
+        const bool fused_plan = T > 0 && nblk <= PLAN_FUSED_MAX_BLOCKS;
+        if (fused_plan) {
+            prof_mark(h, MOE_B200_STAGE_PLAN, true, s);  // an empty stage, not a stale one
+            prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
+        } else {
+            prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
+            plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off, h->tile_start,
+                                          h->blk_base);
+            prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
+            h->last_launches++;
+        }
         if (T > 0) {
             prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
             permute_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(
                 t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb, h->topk_i, h->blk_base, h->slot_of,
-                h->row_token, h->xs, h->status);
+                h->row_token, h->xs, h->status, fused_plan ? h->blk_hist : nullptr, nblk, bn_local, h->cnt,
+                h->off, h->tile_start);
             prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
             h->last_launches++;
         }
@@ -1433,10 +1457,10 @@ moe_b200_status moe_b200_unpack_resident(moe_b200_handle h, int layer, int local
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (which == 1)
         mxfp4_unpack_resident_kernel<<<dim3(h->ks1, h->m_tiles1), TILE_M, 0, s>>>(
-            lw.w1 + local_expert * h->stride1, 2 * I, H, out_bf16);
+            lw.w1 + local_expert * h->stride1, lw.rscale1 + (size_t)local_expert * 2 * I, 2 * I, H, out_bf16);
     else
         mxfp4_unpack_resident_kernel<<<dim3(h->ks2, h->m_tiles2), TILE_M, 0, s>>>(
-            lw.w2 + local_expert * h->stride2, H, I, out_bf16);
+            lw.w2 + local_expert * h->stride2, lw.rscale2 + (size_t)local_expert * H, H, I, out_bf16);
     CU_TRY(h, cudaGetLastError());
     return MOE_B200_OK;
 }

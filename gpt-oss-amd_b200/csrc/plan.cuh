@@ -66,17 +66,80 @@ plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __re
     plan_body(blk_hist, nblk, E, bn, cnt, off, tile_start, blk_base, s_cnt);
 }
 
+// Most routing blocks for which the permute kernel plans by itself (below).
+constexpr int PLAN_FUSED_MAX_BLOCKS = 32;
+
 // Stable placement of every (token, k) assignment into its expert's row range
 // and the row gather x[token] -> xs[row] as bf16 (fp32 input is rounded here:
 // src/hip/BLAS.hip:32-40).  grid = (routing blocks of RB tokens, S): the S
 // blocks of a routing block split its assignments, so that a batch of a few
 // thousand tokens still puts several blocks on every SM (the copy is bound by
 // loads in flight, not by the arithmetic).
+// Small batches (blk_hist != nullptr, at most PLAN_FUSED_MAX_BLOCKS routing blocks):
+// no plan kernel runs before this one; every block sums the per-block histograms
+// itself (a few KB from L2) to find the first row of its own routing block for every
+// expert, and block (0, 0) writes cnt / off / tile_start for the GEMMs.  One launch
+// and one dependent kernel start less on the latency-bound decode path.
 __global__ void __launch_bounds__(256)
 permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, int E, int rb,
                const int* __restrict__ topk_i, const int* __restrict__ blk_base,
                int* __restrict__ slot_of, int* __restrict__ row_token,
-               uint16_t* __restrict__ xs_out, int* __restrict__ status) {
+               uint16_t* __restrict__ xs_out, int* __restrict__ status,
+               const int* __restrict__ blk_hist, int nblk, int bn, int* __restrict__ cnt,
+               int* __restrict__ off, int* __restrict__ tile_start) {
+    __shared__ int s_base[256];
+    if (blk_hist) {
+        __shared__ int s_tot[256];
+        const int e = threadIdx.x;
+        int before = 0;
+        if (e < E) {
+            int total = 0;
+            for (int b = 0; b < nblk; b++) {
+                const int v = blk_hist[(size_t)b * E + e];
+                before += (b < (int)blockIdx.x) ? v : 0;
+                total += v;
+            }
+            s_tot[e] = total;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // exclusive prefix over the experts (and over their tile counts), one warp
+            const bool writer = blockIdx.x == 0 && blockIdx.y == 0;
+            int carry_o = 0, carry_t = 0;
+            for (int e0 = 0; e0 < E; e0 += 32) {
+                const int i = e0 + (int)threadIdx.x;
+                const int c = i < E ? s_tot[i] : 0;
+                const int nt = (c + bn - 1) / bn;
+                int so = c, stl = nt;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int uo = __shfl_up_sync(0xffffffffu, so, d), ut = __shfl_up_sync(0xffffffffu, stl, d);
+                    if ((int)threadIdx.x >= d) {
+                        so += uo;
+                        stl += ut;
+                    }
+                }
+                if (i < E) {
+                    s_base[i] = carry_o + so - c;
+                    if (writer) {
+                        cnt[i] = c;
+                        off[i] = carry_o + so - c;
+                        tile_start[i] = carry_t + stl - nt;
+                    }
+                }
+                carry_o += __shfl_sync(0xffffffffu, so, 31);
+                carry_t += __shfl_sync(0xffffffffu, stl, 31);
+            }
+            if (writer && threadIdx.x == 0) {
+                off[E] = carry_o;
+                tile_start[E] = carry_t;
+            }
+        }
+        __syncthreads();
+        if (e < E)
+            s_base[e] += before;
+        __syncthreads();
+    }
     __shared__ int s_e[RB * 8];
     __shared__ int s_pos[RB * 8];
     const int t0 = blockIdx.x * rb;  // rb <= RB tokens per block, the routing kernel's block size
@@ -103,7 +166,7 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
             int rank = 0;
             for (int j = 0; j < a; j++)
                 rank += (s_e[j] == e);
-            pos = blk_base[(size_t)blockIdx.x * E + e] + rank;
+            pos = (blk_hist ? s_base[e] : blk_base[(size_t)blockIdx.x * E + e]) + rank;
             slot_of[(size_t)t0 * K + a] = pos;
             row_token[pos] = t0 + a / K;
         }

@@ -45,7 +45,8 @@ constexpr int RMLD = RMK + 8;    // bf16 per smem row: conflict-free fragment lo
 constexpr int RTHREADS = 256;
 
 // Stages of the cp.async ring.  Short blocks (small batches: at most a block or two per
-// SM) take as many as fit in ~200 KB of shared memory, at most 12; the 64-token blocks
+// SM, each a chain of H / 64 dependent chunks whose length in time is the number of
+// load round trips) take as many as fit in ~200 KB of shared memory, at most 28; the 64-token blocks
 // of large batches stay under half of it so that two blocks share an SM and a batch of
 // 16384 tokens (256 blocks) runs as one wave.
 template <int NT, int MT>
@@ -53,7 +54,7 @@ __host__ __device__ constexpr int route_tc_stages() {
     constexpr int stage_bytes = (16 * MT + 32 * NT) * RMLD * 2;
     constexpr int budget = (MT == 4 ? 100 : 200) * 1024;
     constexpr int fit = budget / stage_bytes;
-    return fit > 12 ? 12 : (fit < 3 ? 3 : fit);
+    return fit > 28 ? 28 : (fit < 3 ? 3 : fit);
 }
 
 // Shared memory of one block: the stages (reused for the logits after the K loop)

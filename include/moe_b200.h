@@ -109,8 +109,12 @@ moe_b200_status moe_b200_set_router(moe_b200_handle h, int layer, const void* w_
  * rows of mlp1 gate/up interleaved (src/run.cpp:667-670).  `first_expert` is a
  * GLOBAL expert index; the n experts must lie inside this rank's shard.  Host
  * or device pointers.  The library re-tiles the bytes for its kernels; the
- * values they decode to are unchanged.  Scale bytes above 128 (block scales
- * above 2) are rejected with MOE_B200_ERR_UNSUPPORTED.
+ * values they decode to are unchanged.  Every e8m0 scale byte is accepted, as by
+ * dequantize_fp4 (export_model_bin.py:125-129); the one limit: inside ONE weight
+ * row the scale bytes of the blocks that hold a non-zero code may span at most
+ * 128 binades (the row is kept with an exponent shift that the GEMM applies to
+ * its fp32 accumulator).  A row outside that is rejected with
+ * MOE_B200_ERR_UNSUPPORTED and the experts of the call stay unset.
  * Replaces the expert part of src/model.cpp:141-186,365-399. */
 moe_b200_status moe_b200_set_experts_mxfp4(moe_b200_handle h, int layer, int first_expert, int n,
                                            const uint8_t* blocks1, const uint8_t* scales1,

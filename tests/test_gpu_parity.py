@@ -55,13 +55,21 @@ def test_mxfp4_unpack_full_size_matrix():
     assert np.array_equal(out, oracle.mxfp4_dequant_bf16(blocks.numpy(), scales.numpy()))
 
 
-@pytest.mark.parametrize("lo,hi", [(-8, -4), (-127, 1)])
+@pytest.mark.parametrize("lo,hi", [(-8, -4), (-127, 1), (0, 128), (-127, 128)])
 def test_resident_decode_is_bit_exact(lo, hi):
-    """The decode the GEMM main loops use (one bf16x2 multiply per pair), applied
-    to the re-tiled resident weights, against the oracle -- benchmark scale range
-    and the whole supported range of scale bytes 0..128."""
+    """The decode the GEMM main loops use (one bf16x2 multiply per pair, times the
+    row's exponent shift), applied to the re-tiled resident weights, against the
+    oracle -- benchmark scale range, scale bytes 0..128 (no shift), 127..255 and
+    the whole range 0..255 with every row's spread held to 128 binades."""
     shape = pkg.MoEShape(hidden=192, intermediate=128, n_experts=4, top_k=2)
     lw = synth.make_layer(shape, seed=11, scale_lo=lo, scale_hi=hi)
+    if hi - lo > 128:
+        # every row draws its own window of 129 consecutive scale bytes
+        rng = np.random.default_rng(5)
+        for sc in (lw.scales1, lw.scales2):
+            base = rng.integers(0, 256 - 128, size=sc.shape[:2] + (1,))
+            sc[...] = (base + rng.integers(0, 129, size=sc.shape)).astype(np.uint8)
+        assert lw.scales1.max() > 200 and lw.scales1.min() < 20
     with pkg.MoEEngine(shape, max_tokens=8) as eng:
         eng.load_layer(0, lw)
         for e in range(shape.n_experts):
@@ -71,15 +79,45 @@ def test_resident_decode_is_bit_exact(lo, hi):
             assert np.array_equal(w2, oracle.mxfp4_dequant_bf16(lw.blocks2[e], lw.scales2[e]))
 
 
-def test_scale_bytes_above_128_are_rejected():
+def test_row_with_scale_spread_above_128_is_rejected():
+    """One weight row may span 128 binades of block scales; a block of zeros does not count."""
     shape = pkg.MoEShape(hidden=128, intermediate=64, n_experts=4, top_k=2)
     lw = synth.make_layer(shape, seed=1)
-    lw.scales2[1, 3, 0] = 129
+    lw.scales2[1, 3, 0] = 200
+    lw.scales2[1, 3, 1] = 71
+    lw.blocks2[1, 3, 1, :] = 0x11   # non-zero codes under the small scale
     with pkg.MoEEngine(shape, max_tokens=8) as eng:
         with pytest.raises(capi.MoEError) as ei:
             eng.load_layer(0, lw)
         assert ei.value.status == capi.ERR_UNSUPPORTED
         assert eng.device_status() == 0
+        lw.blocks2[1, 3, 1, :] = 0x80   # only zeros (of either sign) under it: representable
+        eng.load_layer(0, lw)
+        w2 = _bits(eng.unpack_resident(0, 1, 2))
+        assert np.array_equal(w2, oracle.mxfp4_dequant_bf16(lw.blocks2[1], lw.scales2[1]))
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_block_with_large_scale_bytes(impl):
+    """Scale bytes above 128 on the GEMM path (rows kept with an exponent shift).
+    Gate/up matrix: every block scale raised by 2^10 (bytes 129..133) and the tokens
+    scaled down by 2^10, so the pre-activations keep their usual size: against the
+    oracle.  Down matrix: raising every block scale by 2^9 (bytes 128..132, rows with and
+    without a shift) must multiply the output by exactly 2^9 (zero bias)."""
+    shape = pkg.MoEShape(hidden=128, intermediate=64, n_experts=8, top_k=2)
+    lw = synth.make_layer(shape, seed=21)
+    lw.scales1 += 10
+    assert lw.scales1.min() == 129
+    x_bits = synth.bf16_bits(torch.from_numpy(synth.bf16_bits_to_f32(synth.make_tokens(96, 128, seed=2)) * 2.0 ** -10))
+    ref = oracle_case(lw, x_bits)
+    res = run_gpu(shape, lw, x_bits, impl)
+    print(compare(res, ref, 2, "scales1 + 10"))
+    lw.bias2[...] = 0
+    small = run_gpu(shape, lw, x_bits, impl, want_h=False)["out"]
+    lw.scales2 += 9
+    assert lw.scales2.min() == 128 and lw.scales2.max() == 132
+    big = run_gpu(shape, lw, x_bits, impl, want_h=False)["out"]
+    assert np.array_equal(big, small * np.float32(512.0))
 
 
 # --------------------------------------------------------------------------
