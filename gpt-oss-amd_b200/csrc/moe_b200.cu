@@ -23,6 +23,7 @@
 #include "mxfp4.cuh"
 #include "plan.cuh"
 #include "route.cuh"
+#include "route_tma.cuh"
 
 using namespace moe;
 
@@ -40,6 +41,8 @@ struct LayerWeights {
     float* rscale1 = nullptr;      // [n_local, 2I]  2^shift of every gate/up weight row (mxfp4_row_shift_kernel)
     float* rscale2 = nullptr;      // [n_local, H]
     bool router_set = false;
+    CUtensorMap map_router{};      // over w_router: box {64 columns, 32 ceil-pow2(E / 32) rows} (route_tma_kernel)
+    bool map_router_ok = false;
     std::vector<char> expert_set;
 };
 
@@ -159,6 +162,33 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn_cached = nullptr;
+    if (!fn_cached) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && fn &&
+            qres == cudaDriverEntryPointSuccess)
+            fn_cached = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    return fn_cached;
+}
+
+// bf16 [rows, cols] row-major, box {64 columns, box_rows}, 128-byte swizzle.  False when
+// the driver refuses (the caller then keeps the cp.async router).
+bool encode_rows_map(CUtensorMap* m, const void* base, int cols, int rows, int box_rows) {
+    EncodeTiledFn encode = tensor_map_encoder();
+    if (!encode || rows <= 0 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || cols % 64 != 0)
+        return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 moe_b200_status make_maps(moe_b200_handle h, tc5::TensorMaps* maps, void* base, int cols, int rows) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -234,6 +264,8 @@ struct RouteArgs {
     int* topk_i;
     float* topk_w;
     int* blk_hist;
+    const CUtensorMap* map_w;  // over the router rows, or null: only the cp.async kernel can run
+    int* status;               // the handle's status word (route_tma_kernel's bounded waits)
 };
 
 template <int NT, int MT, bool XF32>
@@ -257,6 +289,31 @@ cudaError_t launch_route_tc(int dev, const RouteArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+int g_route_tma_attr[MAX_DEVICES];  // bit per (NT, MT) instantiation of route_tma_kernel
+
+// The TMA-fed router (route_tma.cuh).  cudaErrorNotSupported = no tensor map could be
+// made for these rows (unaligned pointer, old driver): the caller falls back.
+template <int NT, int MT>
+cudaError_t launch_route_tma(int dev, const RouteArgs& a, cudaStream_t st) {
+    constexpr int bit = 1 << ((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (MT == 1 ? 0 : MT == 2 ? 1 : 2));
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return cudaErrorInvalidDevice;
+    CUtensorMap map_x;
+    if (!a.map_w || !encode_rows_map(&map_x, a.x, a.H, a.T, 16 * MT))
+        return cudaErrorNotSupported;
+    if (!(g_route_tma_attr[dev] & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(route_tma_kernel<NT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)route_tma_smem_bytes<NT, MT>());
+        if (e != cudaSuccess)
+            return e;
+        g_route_tma_attr[dev] |= bit;
+    }
+    const int nblk = ceil_div(a.T, 16 * MT);
+    route_tma_kernel<NT, MT><<<nblk, RTHREADS, route_tma_smem_bytes<NT, MT>(), st>>>(
+        map_x, *a.map_w, a.T, a.H, a.b_router, a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist, a.status);
+    return cudaGetLastError();
+}
+
 // rb = rows per routing block as route_block_tokens() chose them (fp32 rows: 16).
 cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
     const int nt = ceil_div(a.E, 32);
@@ -271,27 +328,42 @@ cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
             return launch_route_tc<4, 1, true>(dev, a, st);
         return launch_route_tc<8, 1, true>(dev, a, st);
     }
+    // bf16 rows: the TMA-fed kernel where a tensor map over the rows can be made
+#define ROUTE_TRY_TMA(NT_, MT_)                                              \
+    do {                                                                     \
+        const cudaError_t e_ = launch_route_tma<NT_, MT_>(dev, a, st);       \
+        if (e_ != cudaErrorNotSupported)                                     \
+            return e_;                                                       \
+    } while (0)
 #define ROUTE_CASE(NT_)                                         \
     do {                                                        \
-        if (rb == 16)                                           \
+        if (rb == 16) {                                         \
+            ROUTE_TRY_TMA(NT_, 1);                              \
             return launch_route_tc<NT_, 1, false>(dev, a, st);  \
-        if (rb == 32)                                           \
+        }                                                       \
+        if (rb == 32) {                                         \
+            ROUTE_TRY_TMA(NT_, 2);                              \
             return launch_route_tc<NT_, 2, false>(dev, a, st);  \
+        }                                                       \
     } while (0)
     if (nt <= 1) {
         ROUTE_CASE(1);
+        ROUTE_TRY_TMA(1, 4);
         return launch_route_tc<1, 4, false>(dev, a, st);
     }
     if (nt <= 2) {
         ROUTE_CASE(2);
+        ROUTE_TRY_TMA(2, 4);
         return launch_route_tc<2, 4, false>(dev, a, st);
     }
     if (nt <= 4) {
         ROUTE_CASE(4);
+        ROUTE_TRY_TMA(4, 4);
         return launch_route_tc<4, 4, false>(dev, a, st);
     }
     ROUTE_CASE(8);
 #undef ROUTE_CASE
+#undef ROUTE_TRY_TMA
     return cudaErrorInvalidValue;
 }
 
@@ -732,6 +804,12 @@ moe_b200_status moe_b200_set_router(moe_b200_handle h, int layer, const void* w_
     CU_TRY(h, cudaMemcpy(lw.w_router, w_bf16, E * H * 2, cudaMemcpyDefault));
     CU_TRY(h, cudaMemcpy(lw.b_router, bias, E * 4, cudaMemcpyDefault));
     lw.router_set = true;
+    {
+        int nt = 1;
+        while (nt * 32 < (int)E)
+            nt *= 2;
+        lw.map_router_ok = nt <= 8 && encode_rows_map(&lw.map_router, lw.w_router, (int)H, (int)E, 32 * nt);
+    }
     return MOE_B200_OK;
 }
 
@@ -853,6 +931,12 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
         return fail(h, MOE_B200_ERR_INVALID, "the fused norm takes the fp32 residual stream");
     if (n_tokens > 0 && (!t || !out))
         return fail(h, MOE_B200_ERR_INVALID, "null activation / output pointer");
+    // the kernels move rows 16 bytes at a time: a pointer off that boundary would be a
+    // misaligned-address fault on the GPU, so it is refused here
+    if (n_tokens > 0 && ((reinterpret_cast<uintptr_t>(t) | reinterpret_cast<uintptr_t>(out) |
+                          reinterpret_cast<uintptr_t>(rms_w)) & 15u) != 0)
+        return fail(h, MOE_B200_ERR_INVALID,
+                    "activation, output and norm-weight pointers must be 16-byte aligned");
     LayerWeights& lw = h->layers[layer];
     if (!lw.router_set)
         return fail(h, MOE_B200_ERR_NOT_LOADED, "router weights of this layer were not set");
@@ -887,7 +971,7 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
             t_dtype = MOE_B200_DTYPE_BF16;
         }
         RouteArgs ra{t, 0, T, H, lw.w_router, lw.b_router, E, K, router_score_out, h->topk_i, h->topk_w,
-                     h->blk_hist};
+                     h->blk_hist, lw.map_router_ok ? &lw.map_router : nullptr, h->status};
         CU_TRY(h, launch_route(c.device, ra, rb, s));
         prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
         h->last_launches++;
@@ -1392,6 +1476,9 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
         return fail(nullptr, MOE_B200_ERR_INVALID, "moe_b200_route_noalloc: null pointer");
     if (t_dtype != MOE_B200_DTYPE_F32 && t_dtype != MOE_B200_DTYPE_BF16)
         return fail(nullptr, MOE_B200_ERR_INVALID, "moe_b200_route_noalloc: unknown activation dtype");
+    if (((reinterpret_cast<uintptr_t>(t) | reinterpret_cast<uintptr_t>(w_router_bf16)) & 15u) != 0)
+        return fail(nullptr, MOE_B200_ERR_INVALID,
+                    "moe_b200_route_noalloc: activation and router pointers must be 16-byte aligned");
     if (n_tokens <= 0 || n_tokens > MOE_B200_ROUTE_NOALLOC_MAX_TOKENS)
         return fail(nullptr, MOE_B200_ERR_INVALID,
                     "moe_b200_route_noalloc: n_tokens must be in 1.." +
@@ -1434,7 +1521,7 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
     const int nblk = ceil_div(n_tokens, rb);
     RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, n_tokens, hidden_dim,
                  static_cast<const uint16_t*>(w_router_bf16), b_router, n_experts, experts_per_token,
-                 nullptr, topk_i_out, topk_w_out, blk_hist};
+                 nullptr, topk_i_out, topk_w_out, blk_hist, nullptr, nullptr};
     CU_TRY(nullptr, launch_route(dev, ra, rb, st));
     plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, n_experts, 1, expert_counts_out, expert_offsets_out,
                                    tile_start, blk_base);

@@ -152,6 +152,8 @@ moe_b200_status moe_b200_load_experts_file(moe_b200_handle h, const char* path, 
  *                [n_tokens, E] f32 / [n_tokens, K] i32 / [n_tokens, K] f32: the
  *                engine's observable side buffers (include/model.hpp:132-134);
  *                topk_w is after the softmax
+ * `t` and `out` must be 16-byte aligned (rows are moved 16 bytes at a time); a
+ * pointer that is not is refused with MOE_B200_ERR_INVALID.
  * With ep_size > 1 every rank must call this for the same layer in the same
  * order (n_tokens may differ per rank, 0 included). */
 moe_b200_status moe_b200_forward(moe_b200_handle h, int layer, const void* t, int t_dtype,

@@ -470,3 +470,24 @@ def test_router_indices_at_full_width_large_batch():
     assert mism == 0
     assert err < 2e-6
     assert np.abs(res["topk_w"][ok] - tv[ok]).max() < 1e-5
+
+
+def test_unaligned_pointers_are_refused():
+    """Rows move 16 bytes at a time; a pointer off that boundary is an argument error,
+    not a fault on the GPU."""
+    shape = pkg.MoEShape(hidden=128, intermediate=64, n_experts=4, top_k=2)
+    lw = synth.make_layer(shape, seed=1)
+    with pkg.MoEEngine(shape, max_tokens=16) as eng:
+        eng.load_layer(0, lw)
+        flat = torch.zeros(8 * 128 + 8, dtype=torch.bfloat16, device="cuda")
+        good = flat[:8 * 128].view(8, 128)
+        bad = flat[1:1 + 8 * 128].view(8, 128)
+        eng.forward(0, good)
+        with pytest.raises(capi.MoEError) as ei:
+            eng.forward(0, bad)
+        assert ei.value.status == capi.ERR_INVALID
+        out_flat = torch.zeros(8 * 128 + 4, dtype=torch.float32, device="cuda")
+        with pytest.raises(capi.MoEError):
+            eng.forward(0, good, out=out_flat[1:1 + 8 * 128].view(8, 128))
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
