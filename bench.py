@@ -59,11 +59,12 @@ METRIC = "moe_layer_tokens_per_s"
 # only for the single-GPU shape the capture covers (a rank of an N-GPU run does 1/N of the
 # work: no capture, no figure).
 NCU_TRAFFIC = {
-    "decode20b": dict(bytes=296.3e6, source="ncu capture of this launch: one layer, 256 tokens "
-                                            "(profiles/expert_gemm_pair_swap_ncu_full.md)"),
+    "decode20b": dict(bytes=296.0e6, source="ncu capture of this launch: one layer, 256 tokens "
+                                            "(profiles/expert_gemm_ts_layer20b_256tok_ncu_full.md)"),
+    "layer20b": dict(bytes=None, source="not captured at 64 tokens"),
     "prefill120b": dict(bytes=1.80e9, source="ncu capture of the 20b-shaped layer at 2048 tokens, scaled to this "
                                              "launch by the units processed: weight bytes x4 (128 experts), row "
-                                             "bytes x8 (profiles/expert_gemm_pair_swap_ncu_full.md)"),
+                                             "bytes x8 (profiles/expert_gemm_pair_prefill20b_zipf_2048tok_ncu_full.md)"),
 }
 
 

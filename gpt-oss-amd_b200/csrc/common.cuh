@@ -138,6 +138,18 @@ __host__ __device__ __forceinline__ uint32_t mxfp4_decode_exact(uint32_t code, u
 
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may start while the kernel before it on the stream is still running; it
+// does its own set-up (shared-memory init, barriers, tensor-memory allocation) and calls
+// pdl_wait() before it touches anything that kernel wrote -- the wait returns when the
+// whole previous grid has completed and its memory is visible.  pdl_trigger() lets the
+// NEXT kernel start its own set-up early; it orders nothing.  Both are no-ops in a
+// kernel launched the ordinary way.  Every kernel of the forward path calls both, in
+// this order, before its first global access that depends on an earlier kernel, and
+// writes nothing to global memory before the wait.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Clamped SwiGLU (src/run.cpp:673-689, src/hip/moe.hip:186-191): the gate has no
 // lower clamp.
 __device__ __forceinline__ float swiglu(float gate, float up, float alpha, float limit) {

@@ -63,6 +63,8 @@ plan_publish_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, i
                     int* __restrict__ off, int* __restrict__ tile_start, int* __restrict__ blk_base,
                     int G, int rank, Table tb, int seq) {
     __shared__ int s_cnt[256];
+    pdl_trigger();
+    pdl_wait();
     plan_body(blk_hist, nblk, E, bn, cnt, off, tile_start, blk_base, s_cnt);
     // s_cnt is complete for every thread here (plan_body ends behind a barrier)
     for (int i = threadIdx.x; i < G * E; i += blockDim.x) {
@@ -98,6 +100,8 @@ permute_to_peers_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, 
     __shared__ int s_tot[256];
     __shared__ int s_base[256];
     __shared__ int s_ok;
+    pdl_trigger();
+    pdl_wait();
     const int t0 = blockIdx.x * rb;
     const int n_assign = rb * K;
     for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {

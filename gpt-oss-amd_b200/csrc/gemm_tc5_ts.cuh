@@ -195,6 +195,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < WS; s++) {
             mbar_init(bar_w_full(s), 1);
@@ -211,13 +212,16 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
         *abort_flag = 0;
         fence_barrier_init();
     }
+    if (warp == MMA_WARP)
+        tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    // everything above is this CTA's own set-up; what follows reads the plan, the token
+    // rows and the intermediate that earlier kernels of the call wrote
+    pdl_wait();
     for (int i = threadIdx.x; i <= E; i += N_THREADS) {
         s_tables[i] = g_off[i];
         s_tables[(MAX_LOCAL_EXPERTS + 1) + i] = (i < E) ? g_cnt[i] : 0;
         s_tables[2 * (MAX_LOCAL_EXPERTS + 1) + i] = g_tile_start[i];
     }
-    if (warp == MMA_WARP)
-        tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

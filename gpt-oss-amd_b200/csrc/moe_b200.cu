@@ -144,6 +144,31 @@ bool is_device_pointer(const void* p) {
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
+// Programmatic dependent launch (pdl_wait / pdl_trigger in common.cuh) for the kernels
+// of a single-GPU call: each may start its set-up while the kernel before it drains.
+// MOE_B200_NO_PDL=1 in the environment switches it off (a debugging aid: the kernels
+// then run strictly one after the other, as on the expert-parallel paths).
+bool pdl_enabled() {
+    static const bool on = std::getenv("MOE_B200_NO_PDL") == nullptr;
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <typename T>
 moe_b200_status dev_alloc(moe_b200_handle h, T** p, size_t n_elems) {
     void* q = nullptr;
@@ -266,6 +291,7 @@ struct RouteArgs {
     int* blk_hist;
     const CUtensorMap* map_w;  // over the router rows, or null: only the cp.async kernel can run
     int* status;               // the handle's status word (route_tma_kernel's bounded waits)
+    bool pdl;                  // launch as a programmatic dependent of the kernel before it
 };
 
 template <int NT, int MT, bool XF32>
@@ -283,10 +309,11 @@ cudaError_t launch_route_tc(int dev, const RouteArgs& a, cudaStream_t st) {
         g_route_attr[dev] |= bit;
     }
     const int nblk = ceil_div(a.T, 16 * MT);
-    route_tc_kernel<NT, MT, XF32><<<nblk, RTHREADS, route_tc_smem_bytes<NT, MT>(), st>>>(
-        a.x, a.T, a.H, a.w_router, a.b_router, a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist);
     // a launch that failed must not be followed by kernels that consume its output
-    return cudaGetLastError();
+    const cudaError_t e = launch_kernel(a.pdl, route_tc_kernel<NT, MT, XF32>, dim3(nblk), dim3(RTHREADS),
+                                        route_tc_smem_bytes<NT, MT>(), st, a.x, a.T, a.H, a.w_router, a.b_router,
+                                        a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 int g_route_tma_attr[MAX_DEVICES];  // bit per (NT, MT) instantiation of route_tma_kernel
@@ -309,9 +336,10 @@ cudaError_t launch_route_tma(int dev, const RouteArgs& a, cudaStream_t st) {
         g_route_tma_attr[dev] |= bit;
     }
     const int nblk = ceil_div(a.T, 16 * MT);
-    route_tma_kernel<NT, MT><<<nblk, RTHREADS, route_tma_smem_bytes<NT, MT>(), st>>>(
-        map_x, *a.map_w, a.T, a.H, a.b_router, a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist, a.status);
-    return cudaGetLastError();
+    const cudaError_t e = launch_kernel(a.pdl, route_tma_kernel<NT, MT>, dim3(nblk), dim3(RTHREADS),
+                                        route_tma_smem_bytes<NT, MT>(), st, map_x, *a.map_w, a.T, a.H, a.b_router,
+                                        a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist, a.status);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // rb = rows per routing block as route_block_tokens() chose them (fp32 rows: 16).
@@ -382,13 +410,15 @@ moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
     cfg.blockDim = dim3(pr::N_THREADS);
     cfg.dynamicSmemBytes = pr::SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = (h->cfg.ep_size == 1 && pdl_enabled()) ? 2 : 1;
     CU_TRY(h, cudaLaunchKernelEx(&cfg, pr::expert_gemm_pair_kernel<MODE>, maps, chunks, stride, ks, m_tiles,
                                  bias, rscale, bias_stride, g_off, g_cnt, g_tile_start, EL, out, out_ld,
                                  out_valid,
@@ -459,14 +489,17 @@ moe_b200_status launch_ts(moe_b200_handle h, const LayerWeights& lw, const tc5::
         h->smem_attr_done |= 32;
     }
     prof_mark(h, MOE_B200_STAGE_GEMM1, true, st);
-    ts::expert_gemm_ts_kernel<0><<<h->n_sms, ts::N_THREADS, ts::SMEM_BYTES, st>>>(
-        maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1, lw.rscale1, 2 * I, g_off, g_cnt,
-        g_tile_start, EL, h->hbuf, I, I, nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
+    const bool pdl = c.ep_size == 1 && pdl_enabled();
+    CU_TRY(h, launch_kernel(pdl, ts::expert_gemm_ts_kernel<0>, dim3(h->n_sms), dim3(ts::N_THREADS),
+                            ts::SMEM_BYTES, st, maps_x, lw.w1, h->stride1, h->ks1, h->m_tiles1, lw.bias1,
+                            lw.rscale1, 2 * I, g_off, g_cnt, g_tile_start, EL, (void*)h->hbuf, I, I,
+                            (const int*)nullptr, pio, c.swiglu_alpha, c.swiglu_limit, h->status));
     prof_mark(h, MOE_B200_STAGE_GEMM1, false, st);
     prof_mark(h, MOE_B200_STAGE_GEMM2, true, st);
-    ts::expert_gemm_ts_kernel<1><<<h->n_sms, ts::N_THREADS, ts::SMEM_BYTES, st>>>(
-        h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2, lw.rscale2, H, g_off, g_cnt,
-        g_tile_start, EL, yout, H, H, row_dst, pio, c.swiglu_alpha, c.swiglu_limit, h->status);
+    CU_TRY(h, launch_kernel(pdl, ts::expert_gemm_ts_kernel<1>, dim3(h->n_sms), dim3(ts::N_THREADS),
+                            ts::SMEM_BYTES, st, h->maps_h, lw.w2, h->stride2, h->ks2, h->m_tiles2, lw.bias2,
+                            lw.rscale2, H, g_off, g_cnt, g_tile_start, EL, (void*)yout, H, H, row_dst, pio,
+                            c.swiglu_alpha, c.swiglu_limit, h->status));
     prof_mark(h, MOE_B200_STAGE_GEMM2, false, st);
     h->last_launches += 2;
     return MOE_B200_OK;
@@ -953,6 +986,7 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
     const int rb = route_block_tokens(T, ceil_div(E, 32));
     const int nblk = ceil_div(T, rb);
     const int bn_local = pick_bn(h, T * K);  // ep_size == 1: the GEMMs run on this rank's own rows
+    const bool pdl = c.ep_size == 1 && pdl_enabled();
     h->last_launches = 0;
     if (!h->prof_external)
         h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
@@ -964,14 +998,15 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
             // bf16 rows every later kernel reads: one pass, norm folded in when asked
             if (H > 4 * RCAST_THREADS * RCAST_MAX_VEC)
                 return fail(h, MOE_B200_ERR_UNSUPPORTED, "fp32 input is supported up to hidden_dim 8192");
-            rows_to_bf16_kernel<<<T, RCAST_THREADS, 0, s>>>(static_cast<const float*>(t), T, H, rms_w,
-                                                           rms_w_dtype == MOE_B200_DTYPE_F32, h->xn);
+            CU_TRY(h, launch_kernel(pdl, rows_to_bf16_kernel, dim3(T), dim3(RCAST_THREADS), 0, s,
+                                    static_cast<const float*>(t), T, H, rms_w,
+                                    (int)(rms_w_dtype == MOE_B200_DTYPE_F32), h->xn));
             h->last_launches++;
             t = h->xn;
             t_dtype = MOE_B200_DTYPE_BF16;
         }
         RouteArgs ra{t, 0, T, H, lw.w_router, lw.b_router, E, K, router_score_out, h->topk_i, h->topk_w,
-                     h->blk_hist, lw.map_router_ok ? &lw.map_router : nullptr, h->status};
+                     h->blk_hist, lw.map_router_ok ? &lw.map_router : nullptr, h->status, pdl};
         CU_TRY(h, launch_route(c.device, ra, rb, s));
         prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
         h->last_launches++;
@@ -1025,17 +1060,18 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
             prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
         } else {
             prof_mark(h, MOE_B200_STAGE_PLAN, true, s);
-            plan_kernel<<<1, 256, 0, s>>>(h->blk_hist, nblk, E, bn_local, h->cnt, h->off, h->tile_start,
-                                          h->blk_base);
+            CU_TRY(h, launch_kernel(pdl, plan_kernel, dim3(1), dim3(256), 0, s, h->blk_hist, nblk, E, bn_local,
+                                    h->cnt, h->off, h->tile_start, h->blk_base));
             prof_mark(h, MOE_B200_STAGE_PLAN, false, s);
             h->last_launches++;
         }
         if (T > 0) {
             prof_mark(h, MOE_B200_STAGE_PERMUTE, true, s);
-            permute_kernel<<<dim3(nblk, permute_split(h, nblk, rb * K)), 256, 0, s>>>(
-                t, t_dtype == MOE_B200_DTYPE_F32, T, H, K, E, rb, h->topk_i, h->blk_base, h->slot_of,
-                h->row_token, h->xs, h->status, fused_plan ? h->blk_hist : nullptr, nblk, bn_local, h->cnt,
-                h->off, h->tile_start);
+            CU_TRY(h, launch_kernel(pdl, permute_kernel, dim3(nblk, permute_split(h, nblk, rb * K)), dim3(256), 0,
+                                    s, t, (int)(t_dtype == MOE_B200_DTYPE_F32), T, H, K, E, rb, h->topk_i,
+                                    h->blk_base, h->slot_of, h->row_token, h->xs, h->status,
+                                    fused_plan ? h->blk_hist : nullptr, nblk, bn_local, h->cnt, h->off,
+                                    h->tile_start));
             prof_mark(h, MOE_B200_STAGE_PERMUTE, false, s);
             h->last_launches++;
         }
@@ -1069,9 +1105,9 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
         // peer mode launches it for T == 0 as well: the wait inside is what orders this
         // rank's next call behind the peers' reads of this one
         prof_mark(h, MOE_B200_STAGE_COMBINE, true, s);
-        combine_kernel<<<T > 0 ? T : 1, 256, 0, s>>>(y_for_combine, T, H, K, h->topk_i, h->topk_w,
-                                                     h->slot_of, out, accumulate, combine_wait,
-                                                     c.ep_size, seq, h->status);
+        CU_TRY(h, launch_kernel(pdl, combine_kernel, dim3(T > 0 ? T : 1), dim3(256), 0, s, y_for_combine, T, H,
+                                K, h->topk_i, h->topk_w, h->slot_of, out, accumulate, combine_wait, c.ep_size,
+                                seq, h->status));
         prof_mark(h, MOE_B200_STAGE_COMBINE, false, s);
         h->last_launches++;
     }
@@ -1521,7 +1557,7 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
     const int nblk = ceil_div(n_tokens, rb);
     RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, n_tokens, hidden_dim,
                  static_cast<const uint16_t*>(w_router_bf16), b_router, n_experts, experts_per_token,
-                 nullptr, topk_i_out, topk_w_out, blk_hist, nullptr, nullptr};
+                 nullptr, topk_i_out, topk_w_out, blk_hist, nullptr, nullptr, false};
     CU_TRY(nullptr, launch_route(dev, ra, rb, st));
     plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, n_experts, 1, expert_counts_out, expert_offsets_out,
                                    tile_start, blk_base);

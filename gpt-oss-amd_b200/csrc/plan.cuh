@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(256)
 plan_kernel(const int* __restrict__ blk_hist, int nblk, int E, int bn, int* __restrict__ cnt,
             int* __restrict__ off, int* __restrict__ tile_start, int* __restrict__ blk_base) {
     __shared__ int s_cnt[256];
+    pdl_trigger();
+    pdl_wait();
     plan_body(blk_hist, nblk, E, bn, cnt, off, tile_start, blk_base, s_cnt);
 }
 
@@ -88,6 +90,8 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
                const int* __restrict__ blk_hist, int nblk, int bn, int* __restrict__ cnt,
                int* __restrict__ off, int* __restrict__ tile_start) {
     __shared__ int s_base[256];
+    pdl_trigger();
+    pdl_wait();
     if (blk_hist) {
         __shared__ int s_tot[256];
         const int e = threadIdx.x;
@@ -208,6 +212,8 @@ combine_kernel(const float* __restrict__ y, int T, int H, int K, const int* __re
                const float* __restrict__ topk_w, const int* __restrict__ slot_of,
                float* __restrict__ out, int accumulate, const int* __restrict__ wait_flags, int G,
                int seq, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     if (wait_flags) {
         if ((int)threadIdx.x < G) {
             const volatile int* f = wait_flags + threadIdx.x;

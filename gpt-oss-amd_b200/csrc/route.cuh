@@ -161,6 +161,8 @@ rows_to_bf16_kernel(const float* __restrict__ x, int T, int H, const void* __res
                     int rms_w_is_f32, uint16_t* __restrict__ out) {
     __shared__ double s_part[RCAST_THREADS / 32];
     __shared__ float s_scale;
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x;
     if (t >= T)
         return;
@@ -260,6 +262,7 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     const int g = lane >> 2, t4 = lane & 3;
     const int mb = warp % MT, ng = warp / MT;  // this warp's m-tile and expert group
     const int t0 = blockIdx.x * RBT;
+    pdl_trigger();
     for (int i = tid; i < 256; i += RTHREADS)
         hist[i] = 0;
 
@@ -339,6 +342,7 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
         for (int i = 0; i < 4; i++)
             run[n][i] = 0.f;
 
+    pdl_wait();  // the rows may come from the kernel before this one
 #pragma unroll
     for (int c = 0; c < S - 1; c++) {
         if (c < n_chunks)

@@ -88,6 +88,7 @@ route_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int g = lane >> 2, t4 = lane & 3;
     const int mb = warp % MT, ng = warp / MT;  // this warp's m-tile and expert group
     const int t0 = blockIdx.x * RBT;
+    pdl_trigger();
     for (int i = tid; i < 256; i += RTHREADS)
         hist[i] = 0;
     if (tid == 0) {
@@ -97,6 +98,7 @@ route_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         fence_barrier_init();
     }
     __syncthreads();
+    pdl_wait();  // the rows may come from the kernel before this one
 
     // Every block walks the K chunks in its own rotation: all blocks read the same
     // router rows, and in lock step they would all ask the same L2 lines at once.
