@@ -23,7 +23,6 @@
 #include "mxfp4.cuh"
 #include "plan.cuh"
 #include "route.cuh"
-#include "route_tma.cuh"
 
 using namespace moe;
 
@@ -41,8 +40,6 @@ struct LayerWeights {
     float* rscale1 = nullptr;      // [n_local, 2I]  2^shift of every gate/up weight row (mxfp4_row_shift_kernel)
     float* rscale2 = nullptr;      // [n_local, H]
     bool router_set = false;
-    CUtensorMap map_router{};      // over w_router: box {64 columns, 32 ceil-pow2(E / 32) rows} (route_tma_kernel)
-    bool map_router_ok = false;
     std::vector<char> expert_set;
 };
 
@@ -145,9 +142,9 @@ bool is_device_pointer(const void* p) {
 }
 
 // Programmatic dependent launch (pdl_wait / pdl_trigger in common.cuh) for the kernels
-// of a single-GPU call: each may start its set-up while the kernel before it drains.
-// MOE_B200_NO_PDL=1 in the environment switches it off (a debugging aid: the kernels
-// then run strictly one after the other, as on the expert-parallel paths).
+// of a small-batch single-GPU call: each may start its set-up while the kernel before
+// it drains.  MOE_B200_NO_PDL=1 in the environment switches it off (a debugging aid:
+// the kernels then run strictly one after the other, as on every other path).
 bool pdl_enabled() {
     static const bool on = std::getenv("MOE_B200_NO_PDL") == nullptr;
     return on;
@@ -186,33 +183,6 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn tensor_map_encoder() {
-    static EncodeTiledFn fn_cached = nullptr;
-    if (!fn_cached) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && fn &&
-            qres == cudaDriverEntryPointSuccess)
-            fn_cached = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-    return fn_cached;
-}
-
-// bf16 [rows, cols] row-major, box {64 columns, box_rows}, 128-byte swizzle.  False when
-// the driver refuses (the caller then keeps the cp.async router).
-bool encode_rows_map(CUtensorMap* m, const void* base, int cols, int rows, int box_rows) {
-    EncodeTiledFn encode = tensor_map_encoder();
-    if (!encode || rows <= 0 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || cols % 64 != 0)
-        return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 moe_b200_status make_maps(moe_b200_handle h, tc5::TensorMaps* maps, void* base, int cols, int rows) {
     void* fn = nullptr;
@@ -289,9 +259,8 @@ struct RouteArgs {
     int* topk_i;
     float* topk_w;
     int* blk_hist;
-    const CUtensorMap* map_w;  // over the router rows, or null: only the cp.async kernel can run
-    int* status;               // the handle's status word (route_tma_kernel's bounded waits)
     bool pdl;                  // launch as a programmatic dependent of the kernel before it
+    int n_sms;                 // SMs of the device, or 0: never split K over a cluster
 };
 
 template <int NT, int MT, bool XF32>
@@ -316,30 +285,52 @@ cudaError_t launch_route_tc(int dev, const RouteArgs& a, cudaStream_t st) {
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-int g_route_tma_attr[MAX_DEVICES];  // bit per (NT, MT) instantiation of route_tma_kernel
+int g_route_cs_attr[MAX_DEVICES];  // bit per (NT, CS) instantiation of the K-split router
 
-// The TMA-fed router (route_tma.cuh).  cudaErrorNotSupported = no tensor map could be
-// made for these rows (unaligned pointer, old driver): the caller falls back.
-template <int NT, int MT>
-cudaError_t launch_route_tma(int dev, const RouteArgs& a, cudaStream_t st) {
-    constexpr int bit = 1 << ((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (MT == 1 ? 0 : MT == 2 ? 1 : 2));
+// Small batches: a cluster of CS CTAs per block of 16 tokens splits K (route.cuh).
+template <int NT, int CS>
+cudaError_t launch_route_split(int dev, const RouteArgs& a, cudaStream_t st) {
+    constexpr int bit = 1 << ((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (CS == 2 ? 0 : CS == 4 ? 1 : 2));
     if (dev < 0 || dev >= MAX_DEVICES)
         return cudaErrorInvalidDevice;
-    CUtensorMap map_x;
-    if (!a.map_w || !encode_rows_map(&map_x, a.x, a.H, a.T, 16 * MT))
-        return cudaErrorNotSupported;
-    if (!(g_route_tma_attr[dev] & bit)) {
-        cudaError_t e = cudaFuncSetAttribute(route_tma_kernel<NT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)route_tma_smem_bytes<NT, MT>());
+    auto kernel = route_tc_kernel<NT, 1, false, CS>;
+    if (!(g_route_cs_attr[dev] & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)route_tc_smem_bytes<NT, 1, CS>());
         if (e != cudaSuccess)
             return e;
-        g_route_tma_attr[dev] |= bit;
+        g_route_cs_attr[dev] |= bit;
     }
-    const int nblk = ceil_div(a.T, 16 * MT);
-    const cudaError_t e = launch_kernel(a.pdl, route_tma_kernel<NT, MT>, dim3(nblk), dim3(RTHREADS),
-                                        route_tma_smem_bytes<NT, MT>(), st, map_x, *a.map_w, a.T, a.H, a.b_router,
-                                        a.E, a.K, a.score_out, a.topk_i, a.topk_w, a.blk_hist, a.status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div(a.T, 16) * CS);
+    cfg.blockDim = dim3(RTHREADS);
+    cfg.dynamicSmemBytes = route_tc_smem_bytes<NT, 1, CS>();
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 2 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a.x, a.T, a.H, a.w_router, a.b_router, a.E, a.K,
+                                             a.score_out, a.topk_i, a.topk_w, a.blk_hist);
     return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <int NT>
+cudaError_t launch_route_short(int dev, const RouteArgs& a, cudaStream_t st) {
+    // as many CTAs per token block as still fit one wave
+    const int nblk = ceil_div(a.T, 16);
+    if (nblk * 8 <= a.n_sms)
+        return launch_route_split<NT, 8>(dev, a, st);
+    if (nblk * 4 <= a.n_sms)
+        return launch_route_split<NT, 4>(dev, a, st);
+    if (nblk * 2 <= a.n_sms)
+        return launch_route_split<NT, 2>(dev, a, st);
+    return launch_route_tc<NT, 1, false>(dev, a, st);
 }
 
 // rb = rows per routing block as route_block_tokens() chose them (fp32 rows: 16).
@@ -356,42 +347,27 @@ cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
             return launch_route_tc<4, 1, true>(dev, a, st);
         return launch_route_tc<8, 1, true>(dev, a, st);
     }
-    // bf16 rows: the TMA-fed kernel where a tensor map over the rows can be made
-#define ROUTE_TRY_TMA(NT_, MT_)                                              \
-    do {                                                                     \
-        const cudaError_t e_ = launch_route_tma<NT_, MT_>(dev, a, st);       \
-        if (e_ != cudaErrorNotSupported)                                     \
-            return e_;                                                       \
-    } while (0)
 #define ROUTE_CASE(NT_)                                         \
     do {                                                        \
-        if (rb == 16) {                                         \
-            ROUTE_TRY_TMA(NT_, 1);                              \
-            return launch_route_tc<NT_, 1, false>(dev, a, st);  \
-        }                                                       \
-        if (rb == 32) {                                         \
-            ROUTE_TRY_TMA(NT_, 2);                              \
+        if (rb == 16)                                           \
+            return launch_route_short<NT_>(dev, a, st);         \
+        if (rb == 32)                                           \
             return launch_route_tc<NT_, 2, false>(dev, a, st);  \
-        }                                                       \
     } while (0)
     if (nt <= 1) {
         ROUTE_CASE(1);
-        ROUTE_TRY_TMA(1, 4);
         return launch_route_tc<1, 4, false>(dev, a, st);
     }
     if (nt <= 2) {
         ROUTE_CASE(2);
-        ROUTE_TRY_TMA(2, 4);
         return launch_route_tc<2, 4, false>(dev, a, st);
     }
     if (nt <= 4) {
         ROUTE_CASE(4);
-        ROUTE_TRY_TMA(4, 4);
         return launch_route_tc<4, 4, false>(dev, a, st);
     }
     ROUTE_CASE(8);
 #undef ROUTE_CASE
-#undef ROUTE_TRY_TMA
     return cudaErrorInvalidValue;
 }
 
@@ -410,15 +386,13 @@ moe_b200_status launch_pair_kernel(moe_b200_handle h, int grid, cudaStream_t st,
     cfg.blockDim = dim3(pr::N_THREADS);
     cfg.dynamicSmemBytes = pr::SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (h->cfg.ep_size == 1 && pdl_enabled()) ? 2 : 1;
+    cfg.numAttrs = 1;
     CU_TRY(h, cudaLaunchKernelEx(&cfg, pr::expert_gemm_pair_kernel<MODE>, maps, chunks, stride, ks, m_tiles,
                                  bias, rscale, bias_stride, g_off, g_cnt, g_tile_start, EL, out, out_ld,
                                  out_valid,
@@ -837,12 +811,6 @@ moe_b200_status moe_b200_set_router(moe_b200_handle h, int layer, const void* w_
     CU_TRY(h, cudaMemcpy(lw.w_router, w_bf16, E * H * 2, cudaMemcpyDefault));
     CU_TRY(h, cudaMemcpy(lw.b_router, bias, E * 4, cudaMemcpyDefault));
     lw.router_set = true;
-    {
-        int nt = 1;
-        while (nt * 32 < (int)E)
-            nt *= 2;
-        lw.map_router_ok = nt <= 8 && encode_rows_map(&lw.map_router, lw.w_router, (int)H, (int)E, 32 * nt);
-    }
     return MOE_B200_OK;
 }
 
@@ -986,7 +954,10 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
     const int rb = route_block_tokens(T, ceil_div(E, 32));
     const int nblk = ceil_div(T, rb);
     const int bn_local = pick_bn(h, T * K);  // ep_size == 1: the GEMMs run on this rank's own rows
-    const bool pdl = c.ep_size == 1 && pdl_enabled();
+    // Programmatic dependent launch pays for small batches (decode20b: 4.20 -> 4.05 ms per
+    // step) and costs about 1 % on large ones (the next kernel's waiting blocks share the
+    // SMs of a GEMM that is bound by instruction issue), so it follows the GEMM choice.
+    const bool pdl = c.ep_size == 1 && pdl_enabled() && bn_local == tc5::ts::BN;
     h->last_launches = 0;
     if (!h->prof_external)
         h->prof_call = (h->prof_next < h->prof_armed) ? h->prof_next++ : -1;
@@ -1006,7 +977,7 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
             t_dtype = MOE_B200_DTYPE_BF16;
         }
         RouteArgs ra{t, 0, T, H, lw.w_router, lw.b_router, E, K, router_score_out, h->topk_i, h->topk_w,
-                     h->blk_hist, lw.map_router_ok ? &lw.map_router : nullptr, h->status, pdl};
+                     h->blk_hist, pdl, h->n_sms};
         CU_TRY(h, launch_route(c.device, ra, rb, s));
         prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
         h->last_launches++;
@@ -1557,7 +1528,7 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
     const int nblk = ceil_div(n_tokens, rb);
     RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, n_tokens, hidden_dim,
                  static_cast<const uint16_t*>(w_router_bf16), b_router, n_experts, experts_per_token,
-                 nullptr, topk_i_out, topk_w_out, blk_hist, nullptr, nullptr, false};
+                 nullptr, topk_i_out, topk_w_out, blk_hist, false, 0};
     CU_TRY(nullptr, launch_route(dev, ra, rb, st));
     plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, n_experts, 1, expert_counts_out, expert_offsets_out,
                                    tile_start, blk_base);

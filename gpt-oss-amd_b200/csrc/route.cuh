@@ -49,19 +49,21 @@ constexpr int RTHREADS = 256;
 // load round trips) take as many as fit in ~200 KB of shared memory, at most 28; the 64-token blocks
 // of large batches stay under half of it so that two blocks share an SM and a batch of
 // 16384 tokens (256 blocks) runs as one wave.
-template <int NT, int MT>
+// A CTA of a K-splitting cluster (CS > 1) walks only 1/CS of the chunks: 8 stages cover them.
+template <int NT, int MT, int CS = 1>
 __host__ __device__ constexpr int route_tc_stages() {
     constexpr int stage_bytes = (16 * MT + 32 * NT) * RMLD * 2;
     constexpr int budget = (MT == 4 ? 100 : 200) * 1024;
     constexpr int fit = budget / stage_bytes;
-    return fit > 28 ? 28 : (fit < 3 ? 3 : fit);
+    constexpr int cap = CS > 1 ? 8 : 28;
+    return fit > cap ? cap : (fit < 3 ? 3 : fit);
 }
 
 // Shared memory of one block: the stages (reused for the logits after the K loop)
 // plus the histogram.
-template <int NT, int MT>
+template <int NT, int MT, int CS = 1>
 constexpr size_t route_tc_smem_bytes() {
-    size_t tiles = (size_t)route_tc_stages<NT, MT>() * (16 * MT + 32 * NT) * RMLD * 2;
+    size_t tiles = (size_t)route_tc_stages<NT, MT, CS>() * (16 * MT + 32 * NT) * RMLD * 2;
     size_t logits = (size_t)(16 * MT) * (32 * NT) * 4;
     return (tiles > logits ? tiles : logits) + 256 * sizeof(int);
 }
@@ -233,7 +235,38 @@ rows_to_bf16_kernel(const float* __restrict__ x, int T, int H, const void* __res
 // a chunk then costs a global-load latency).  Only the handle-free entry point,
 // which has nowhere to put a bf16 copy of the rows, uses it.
 // Grid: ceil(T / (16 MT)) blocks of RTHREADS threads.
-template <int NT, int MT, bool XF32>
+//
+// CS > 1 (small batches only): a thread-block CLUSTER of CS CTAs shares one block of
+// tokens and splits K -- CTA r of the cluster takes the chunks r, r + CS, ... -- so the
+// chain of dependent chunks is CS times shorter and CS times as many SMs pull the rows.
+// Each CTA leaves its partial sums in its own shared memory; after a cluster barrier
+// CTA 0 adds them in rank order through distributed shared memory (a fixed order: the
+// result does not depend on timing), then does bias, top-K, softmax and the histogram
+// as before.  The grid is CS x the number of token blocks.
+__device__ __forceinline__ uint32_t route_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void route_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The float at the same shared-memory address in CTA `rank` of the cluster.  Volatile (it
+// stays behind the cluster barrier, itself a volatile asm) but without a memory clobber:
+// the loads of one element from all ranks are independent and overlap -- a remote
+// shared-memory load takes several hundred cycles.
+__device__ __forceinline__ float route_ld_remote(const float* p, uint32_t rank) {
+    float v;
+    const uint32_t la = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %1, %2;\n\t"
+        "ld.shared::cluster.f32 %0, [ra];\n\t}"
+        : "=f"(v) : "r"(la), "r"(rank));
+    return v;
+}
+
+template <int NT, int MT, bool XF32, int CS = 1>
 __global__ void __launch_bounds__(RTHREADS)
 route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __restrict__ w_router,
                 const float* __restrict__ b_router, int E, int K, float* __restrict__ score_out,
@@ -245,13 +278,14 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     // 8 warps = MT m-tiles x NG expert groups; a warp owns NTW n8 tiles of one m-tile
     constexpr int NG = 8 / MT;
     constexpr int NTW = (N_TILES + NG - 1) / NG;
-    constexpr int S = route_tc_stages<NT, MT>();
+    constexpr int S = route_tc_stages<NT, MT, CS>();
     constexpr int ROWS = RBT + EP;               // rows of a stage: token rows, then router rows
     constexpr int STAGE_ELEMS = ROWS * RMLD;
     constexpr size_t tiles_b = (size_t)S * STAGE_ELEMS * 2;
     constexpr size_t lg_b = (size_t)RBT * EP * 4;
     constexpr int SEGS = (ROWS * 8 + RTHREADS - 1) / RTHREADS;  // 16-byte segments per thread and chunk
     static_assert(S >= 3, "the ring needs at least three stages");
+    static_assert(CS == 1 || (MT == 1 && !XF32), "the K split is for short bf16 blocks");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t* tiles = reinterpret_cast<uint16_t*>(smem_raw);
@@ -261,7 +295,9 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int mb = warp % MT, ng = warp / MT;  // this warp's m-tile and expert group
-    const int t0 = blockIdx.x * RBT;
+    const int crank = CS > 1 ? (int)route_cluster_rank() : 0;  // this CTA's share of K
+    const int tblk = (int)blockIdx.x / CS;                      // its block of tokens
+    const int t0 = tblk * RBT;
     pdl_trigger();
     for (int i = tid; i < 256; i += RTHREADS)
         hist[i] = 0;
@@ -290,13 +326,14 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     }
     // Every block walks the K chunks in its own rotation: all blocks read the same
     // router rows, and in lock step they would all ask the same L2 lines at once.
-    const int n_chunks = H / RMK;  // H is a multiple of 64
-    const int c_rot = (int)((blockIdx.x * 7u) % (unsigned)n_chunks);
+    const int n_chunks_all = H / RMK;  // H is a multiple of 64
+    const int n_chunks = (n_chunks_all - crank + CS - 1) / CS;  // this CTA's: crank, crank + CS, ... (may be 0)
+    const int c_rot = n_chunks > 0 ? (int)(((unsigned)tblk * 7u) % (unsigned)n_chunks) : 0;
     auto chunk_col = [&](int c) {
         int k = c + c_rot;
         if (k >= n_chunks)
             k -= n_chunks;
-        return k * RMK;
+        return (crank + k * CS) * RMK;
     };
     auto issue = [&](int c) {  // cp.async of the c-th chunk of this block into its stage
         uint16_t* st = tiles + (c % S) * STAGE_ELEMS;
@@ -413,9 +450,38 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
             for (int i = 0; i < 4; i++) {
                 const int row = mb * 16 + g + 8 * (i >> 1);
                 const int e = nt * 8 + 2 * t4 + (i & 1);
-                lg[row * EP + e] = (e < E) ? run[n][i] + b_router[e] : -INFINITY;
+                if (CS > 1)
+                    lg[row * EP + e] = run[n][i];  // this CTA's share of the sum
+                else
+                    lg[row * EP + e] = (e < E) ? run[n][i] + b_router[e] : -INFINITY;
             }
         }
+    }
+    if (CS > 1) {
+        route_cluster_sync();  // every CTA's partial sums are in its shared memory
+        if (crank == 0) {
+            constexpr int PER = RBT * EP / RTHREADS;  // elements per thread: 2 NT
+            float part[PER][CS];
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                part[j][0] = lg[tid + j * RTHREADS];
+#pragma unroll
+                for (int r = 1; r < CS; r++)
+                    part[j][r] = route_ld_remote(lg + tid + j * RTHREADS, (uint32_t)r);
+            }
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                float v = part[j][0];
+#pragma unroll
+                for (int r = 1; r < CS; r++)
+                    v += part[j][r];  // rank order: the sum does not depend on timing
+                const int e = (tid + j * RTHREADS) % EP;
+                lg[tid + j * RTHREADS] = (e < E) ? v + b_router[e] : -INFINITY;
+            }
+        }
+        route_cluster_sync();  // the other CTAs' shared memory has been read: they may leave
+        if (crank != 0)
+            return;
     }
     __syncthreads();
     if (score_out) {
@@ -437,7 +503,7 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     }
     __syncthreads();
     for (int e = tid; e < E; e += RTHREADS)
-        blk_hist[(size_t)blockIdx.x * E + e] = hist[e];
+        blk_hist[(size_t)tblk * E + e] = hist[e];
 }
 
 }  // namespace moe

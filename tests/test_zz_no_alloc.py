@@ -65,9 +65,10 @@ def test_route_noalloc_matches_forward_on_two_calls_in_a_row():
             torch.cuda.synchronize()
             ref_cnt = np.array(eng.last_expert_counts())
             ti, tw, cnt, off = _route_noalloc(t, w_router, b_router, shape.n_experts, shape.top_k)
-            # same kernels on the same inputs: identical, not merely close
+            # the same router on the same inputs; the handle's path may split K over a
+            # cluster of CTAs (another order of the fp32 chunk sums): last-bit differences
             assert np.array_equal(ti, ref_i.cpu().numpy()), f"call {call}"
-            assert np.array_equal(tw, ref_w.cpu().numpy()), f"call {call}"
+            assert np.abs(tw - ref_w.cpu().numpy()).max() < 1e-6, f"call {call}"
             assert np.array_equal(cnt, ref_cnt), f"call {call}"
             assert cnt.sum() == T * shape.top_k
             assert np.array_equal(off, np.concatenate([[0], np.cumsum(cnt)])), f"call {call}"
@@ -110,7 +111,8 @@ def test_route_noalloc_interleaved_with_handles_of_other_hidden_sizes():
         _, _, ref_i, ref_w = eng.forward(0, t, side=True)
         torch.cuda.synchronize()
         assert np.array_equal(second[0], ref_i.cpu().numpy())
-        assert np.array_equal(second[1], ref_w.cpu().numpy())
+        # the handle's router may split K over a cluster of CTAs: last-bit differences
+        assert np.abs(second[1] - ref_w.cpu().numpy()).max() < 1e-6
 
 
 def test_route_noalloc_rejects_sizes_beyond_its_fixed_scratch():
