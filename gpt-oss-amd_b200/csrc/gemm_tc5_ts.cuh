@@ -21,9 +21,9 @@
 // with the decoded weights as the UMMA A operand IN TENSOR MEMORY (tcgen05.mma
 // "TS" form: lane = weight row, one 32-bit column = two consecutive bf16 of K,
 // written by the decode warps with tcgen05.st straight from registers) and the
-// token rows as the B operand in shared memory (N = 32 .. 128, a TMA box).  The
-// tensor work is negligible (a 128 x 32 x 64 step is ~70 cycles), shared memory
-// carries only the packed bytes and the small activation tile.
+// token rows as the B operand in shared memory (N = 32 or 64, a TMA box).  The
+// tensor work is small (the four MMAs of a 128 x 32 x 64 chunk issue in ~100
+// cycles), shared memory carries only the packed bytes and the small activation tile.
 //
 // One persistent CTA per SM walks work items (expert, 128-row weight tile, tile
 // of up to 64 token rows).  A pipeline STEP covers CS = 6 chunks of 64 K-columns
@@ -502,7 +502,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             tc_fence_after();
             const int mt = ti.mt;
             const float* be = bias + (size_t)ti.e * bias_stride;
-                const float* rse = rscale + (size_t)ti.e * bias_stride;  // 2^shift of every weight row
+            const float* rse = rscale + (size_t)ti.e * bias_stride;  // 2^shift of every weight row
             const int m = mt * TILE_M + row;
             const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(set * BN);
             if (MODE == 0) {
@@ -548,7 +548,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
                 float* y = static_cast<float*>(outp);
                 float* stage32 = reinterpret_cast<float*>(stage);
                 const float bm = (m < out_rows_valid) ? be[m] : 0.f;
-                    const float rs = (m < out_rows_valid) ? rse[m] : 1.f;
+                const float rs = (m < out_rows_valid) ? rse[m] : 1.f;
                 const int m4 = mt * TILE_M + q * 32 + (lane & 7) * 4;  // columns this lane stores
                 const bool m4_ok = m4 < out_rows_valid;                // the width is a multiple of 4
                 for (int c0 = 0; c0 < ti.n_mma; c0 += 32) {
