@@ -53,7 +53,7 @@ constexpr int RTHREADS = 256;
 template <int NT, int MT, int CS = 1>
 __host__ __device__ constexpr int route_tc_stages() {
     constexpr int stage_bytes = (16 * MT + 32 * NT) * RMLD * 2;
-    constexpr int budget = (MT == 4 ? 100 : 200) * 1024;
+    constexpr int budget = (MT == 4 && CS == 1 ? 100 : 200) * 1024;
     constexpr int fit = budget / stage_bytes;
     constexpr int cap = CS > 1 ? 8 : 28;
     return fit > cap ? cap : (fit < 3 ? 3 : fit);
@@ -236,7 +236,7 @@ rows_to_bf16_kernel(const float* __restrict__ x, int T, int H, const void* __res
 // which has nowhere to put a bf16 copy of the rows, uses it.
 // Grid: ceil(T / (16 MT)) blocks of RTHREADS threads.
 //
-// CS > 1 (small batches only): a thread-block CLUSTER of CS CTAs shares one block of
+// CS > 1 (batches that do not fill the GPU): a thread-block CLUSTER of CS CTAs shares one block of
 // tokens and splits K -- CTA r of the cluster takes the chunks r, r + CS, ... -- so the
 // chain of dependent chunks is CS times shorter and CS times as many SMs pull the rows.
 // Each CTA leaves its partial sums in its own shared memory; after a cluster barrier
@@ -285,7 +285,7 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     constexpr size_t lg_b = (size_t)RBT * EP * 4;
     constexpr int SEGS = (ROWS * 8 + RTHREADS - 1) / RTHREADS;  // 16-byte segments per thread and chunk
     static_assert(S >= 3, "the ring needs at least three stages");
-    static_assert(CS == 1 || (MT == 1 && !XF32), "the K split is for short bf16 blocks");
+    static_assert(CS == 1 || !XF32, "the K split takes bf16 rows");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t* tiles = reinterpret_cast<uint16_t*>(smem_raw);
@@ -460,23 +460,26 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     if (CS > 1) {
         route_cluster_sync();  // every CTA's partial sums are in its shared memory
         if (crank == 0) {
-            constexpr int PER = RBT * EP / RTHREADS;  // elements per thread: 2 NT
-            float part[PER][CS];
+            constexpr int PER = RBT * EP / RTHREADS;  // elements per thread: 2 NT MT
+            constexpr int BATCH = PER < 4 ? PER : 4;  // elements whose remote loads are in flight together
+            for (int j0 = 0; j0 < PER; j0 += BATCH) {
+                float part[BATCH][CS];
 #pragma unroll
-            for (int j = 0; j < PER; j++) {
-                part[j][0] = lg[tid + j * RTHREADS];
+                for (int j = 0; j < BATCH; j++) {
+                    part[j][0] = lg[tid + (j0 + j) * RTHREADS];
 #pragma unroll
-                for (int r = 1; r < CS; r++)
-                    part[j][r] = route_ld_remote(lg + tid + j * RTHREADS, (uint32_t)r);
-            }
+                    for (int r = 1; r < CS; r++)
+                        part[j][r] = route_ld_remote(lg + tid + (j0 + j) * RTHREADS, (uint32_t)r);
+                }
 #pragma unroll
-            for (int j = 0; j < PER; j++) {
-                float v = part[j][0];
+                for (int j = 0; j < BATCH; j++) {
+                    float v = part[j][0];
 #pragma unroll
-                for (int r = 1; r < CS; r++)
-                    v += part[j][r];  // rank order: the sum does not depend on timing
-                const int e = (tid + j * RTHREADS) % EP;
-                lg[tid + j * RTHREADS] = (e < E) ? v + b_router[e] : -INFINITY;
+                    for (int r = 1; r < CS; r++)
+                        v += part[j][r];  // rank order: the sum does not depend on timing
+                    const int e = (tid + (j0 + j) * RTHREADS) % EP;
+                    lg[tid + (j0 + j) * RTHREADS] = (e < E) ? v + b_router[e] : -INFINITY;
+                }
             }
         }
         route_cluster_sync();  // the other CTAs' shared memory has been read: they may leave
