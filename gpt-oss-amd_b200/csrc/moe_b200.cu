@@ -230,44 +230,19 @@ moe_b200_status check_layer(moe_b200_handle h, int layer) {
 constexpr int TC5_BN = 256;                   // token rows per tile of the large-batch GEMM
 constexpr int SMALL_MAX_ROWS_PER_EXPERT = 64; // at most this many rows per expert on average: small-batch GEMM
 
-// Shape of a routing launch: token rows per routing block (16 x the router kernel's MT)
-// and how many CTAs of a cluster split K for it (CS).  Every token block streams the
-// whole router matrix from L2 whatever its height, so the L2 -> SM traffic falls with
-// taller blocks; the K split gives the parallelism back.  Batches above 4736 tokens
-// take tall blocks and no split (they fill the GPU anyway); for the rest the (MT, CS)
-// that moves the fewest bytes per CTA within one wave of `n_sms` CTAs wins.
-// `nt` = ceil(E / 32).  n_sms <= 0: never split (the handle-free entry point).
-int route_block_tokens_large(int T, int nt) {
-    if (T <= 4736)
+// Token rows per routing block (16 x the router kernel's MT).  Measured (E = 128, route
+// stage in ms; block height, CTAs per cluster): 2048 tokens (16,1) 0.030, (32,1) 0.042,
+// (32,2) 0.031, (64,1) 0.079, (64,4) 0.053; 4096 tokens (16,1) 0.054, (32,1) 0.042,
+// (32,2) 0.053, (64,2) 0.062: a block's time grows with its height (more 16-byte
+// copies per thread and chunk in the same dependent chain), so a batch takes the
+// shortest blocks that still run as one wave, and tall blocks only when it must.
+// `nt` = ceil(E / 32).
+int route_block_tokens(int T, int nt) {
+    if (T <= 2368)
         return 16;
     if (T <= 9472 || nt > 4)  // 8 expert tiles: at most 32 rows per block (registers)
         return 32;
     return 64;
-}
-void route_shape(int T, int nt, int n_sms, int* rb, int* cs) {
-    *rb = route_block_tokens_large(T, nt);
-    *cs = 1;
-    if (T > 4736 || n_sms <= 0 || T <= 0)
-        return;
-    long best = -1;
-    for (int mt = 1; mt <= 4; mt *= 2) {
-        if (mt == 4 && nt > 4)
-            continue;
-        const int blocks = ceil_div(T, 16 * mt);
-        int c = 1;
-        for (int t = 8; t > 1; t /= 2)
-            if (blocks * t <= n_sms) {
-                c = t;
-                break;
-            }
-        const long waves = ceil_div(blocks * c, n_sms);
-        const long cost = (long)(16 * mt + 32 * nt) * 64 / c * waves;  // ~ bytes per SM, up to a factor
-        if (best < 0 || cost < best) {
-            best = cost;
-            *rb = 16 * mt;
-            *cs = c;
-        }
-    }
 }
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize belongs to (device, kernel), not to a
@@ -289,6 +264,7 @@ struct RouteArgs {
     float* topk_w;
     int* blk_hist;
     bool pdl;                  // launch as a programmatic dependent of the kernel before it
+    int n_sms;                 // SMs of the device, or 0: never split K over a cluster
 };
 
 template <int NT, int MT, bool XF32>
@@ -313,24 +289,26 @@ cudaError_t launch_route_tc(int dev, const RouteArgs& a, cudaStream_t st) {
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-// A cluster of CS CTAs per block of 16 MT tokens splits K (route.cuh).
-template <int NT, int MT, int CS>
+int g_route_cs_attr[MAX_DEVICES];  // bit per (NT, CS) instantiation of the K-split router
+
+// Small batches: a cluster of CS CTAs per block of 16 tokens splits K (route.cuh).
+template <int NT, int CS>
 cudaError_t launch_route_split(int dev, const RouteArgs& a, cudaStream_t st) {
-    static bool attr_done[MAX_DEVICES];  // per instantiation: the shared-memory size depends on nothing else
+    constexpr int bit = 1 << ((NT == 1 ? 0 : NT == 2 ? 1 : NT == 4 ? 2 : 3) * 3 + (CS == 2 ? 0 : CS == 4 ? 1 : 2));
     if (dev < 0 || dev >= MAX_DEVICES)
         return cudaErrorInvalidDevice;
-    auto kernel = route_tc_kernel<NT, MT, false, CS>;
-    if (!attr_done[dev]) {
+    auto kernel = route_tc_kernel<NT, 1, false, CS>;
+    if (!(g_route_cs_attr[dev] & bit)) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)route_tc_smem_bytes<NT, MT, CS>());
+                                             (int)route_tc_smem_bytes<NT, 1, CS>());
         if (e != cudaSuccess)
             return e;
-        attr_done[dev] = true;
+        g_route_cs_attr[dev] |= bit;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(a.T, 16 * MT) * CS);
+    cfg.gridDim = dim3(ceil_div(a.T, 16) * CS);
     cfg.blockDim = dim3(RTHREADS);
-    cfg.dynamicSmemBytes = route_tc_smem_bytes<NT, MT, CS>();
+    cfg.dynamicSmemBytes = route_tc_smem_bytes<NT, 1, CS>();
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -346,35 +324,24 @@ cudaError_t launch_route_split(int dev, const RouteArgs& a, cudaStream_t st) {
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-template <int NT, int MT>
-cudaError_t launch_route_nm(int dev, const RouteArgs& a, int cs, cudaStream_t st) {
-    switch (cs) {
-        case 1: return launch_route_tc<NT, MT, false>(dev, a, st);
-        case 2: return launch_route_split<NT, MT, 2>(dev, a, st);
-        case 4: return launch_route_split<NT, MT, 4>(dev, a, st);
-        case 8: return launch_route_split<NT, MT, 8>(dev, a, st);
-    }
-    return cudaErrorInvalidValue;
-}
-
 template <int NT>
-cudaError_t launch_route_n(int dev, const RouteArgs& a, int rb, int cs, cudaStream_t st) {
-    if (rb == 16)
-        return launch_route_nm<NT, 1>(dev, a, cs, st);
-    if (rb == 32)
-        return launch_route_nm<NT, 2>(dev, a, cs, st);
-    if constexpr (NT <= 4) {
-        if (rb == 64)
-            return launch_route_nm<NT, 4>(dev, a, cs, st);
-    }
-    return cudaErrorInvalidValue;
+cudaError_t launch_route_short(int dev, const RouteArgs& a, cudaStream_t st) {
+    // as many CTAs per token block as still fit one wave
+    const int nblk = ceil_div(a.T, 16);
+    if (nblk * 8 <= a.n_sms)
+        return launch_route_split<NT, 8>(dev, a, st);
+    if (nblk * 4 <= a.n_sms)
+        return launch_route_split<NT, 4>(dev, a, st);
+    if (nblk * 2 <= a.n_sms)
+        return launch_route_split<NT, 2>(dev, a, st);
+    return launch_route_tc<NT, 1, false>(dev, a, st);
 }
 
-// rb, cs = the launch shape route_shape() chose (fp32 rows: 16, 1).
-cudaError_t launch_route(int dev, const RouteArgs& a, int rb, int cs, cudaStream_t st) {
+// rb = rows per routing block as route_block_tokens() chose them (fp32 rows: 16).
+cudaError_t launch_route(int dev, const RouteArgs& a, int rb, cudaStream_t st) {
     const int nt = ceil_div(a.E, 32);
     if (a.x_is_f32) {
-        if (rb != 16 || cs != 1)
+        if (rb != 16)
             return cudaErrorInvalidValue;
         if (nt <= 1)
             return launch_route_tc<1, 1, true>(dev, a, st);
@@ -384,13 +351,28 @@ cudaError_t launch_route(int dev, const RouteArgs& a, int rb, int cs, cudaStream
             return launch_route_tc<4, 1, true>(dev, a, st);
         return launch_route_tc<8, 1, true>(dev, a, st);
     }
-    if (nt <= 1)
-        return launch_route_n<1>(dev, a, rb, cs, st);
-    if (nt <= 2)
-        return launch_route_n<2>(dev, a, rb, cs, st);
-    if (nt <= 4)
-        return launch_route_n<4>(dev, a, rb, cs, st);
-    return launch_route_n<8>(dev, a, rb, cs, st);
+#define ROUTE_CASE(NT_)                                         \
+    do {                                                        \
+        if (rb == 16)                                           \
+            return launch_route_short<NT_>(dev, a, st);         \
+        if (rb == 32)                                           \
+            return launch_route_tc<NT_, 2, false>(dev, a, st);  \
+    } while (0)
+    if (nt <= 1) {
+        ROUTE_CASE(1);
+        return launch_route_tc<1, 4, false>(dev, a, st);
+    }
+    if (nt <= 2) {
+        ROUTE_CASE(2);
+        return launch_route_tc<2, 4, false>(dev, a, st);
+    }
+    if (nt <= 4) {
+        ROUTE_CASE(4);
+        return launch_route_tc<4, 4, false>(dev, a, st);
+    }
+    ROUTE_CASE(8);
+#undef ROUTE_CASE
+    return cudaErrorInvalidValue;
 }
 
 // Large batches on CTA pairs (gemm_tc5_pair.cuh): cluster launch, one cluster per SM pair.
@@ -725,10 +707,10 @@ moe_b200_status moe_b200_create(const moe_b200_config* cfg, moe_b200_handle* out
     {
         // most routing blocks any batch up to max_tokens can have
         const int nt = ceil_div(E, 32);
-        const int steps[3] = {std::min(c.max_tokens, 4736), std::min(c.max_tokens, 9472), c.max_tokens};
+        const int steps[3] = {std::min(c.max_tokens, 2368), std::min(c.max_tokens, 9472), c.max_tokens};
         h->nblk_cap = 1;
         for (int i = 0; i < 3; i++)
-            h->nblk_cap = std::max(h->nblk_cap, ceil_div(steps[i], route_block_tokens_large(steps[i], nt)));
+            h->nblk_cap = std::max(h->nblk_cap, ceil_div(steps[i], route_block_tokens(steps[i], nt)));
     }
 
     moe_b200_status st = MOE_B200_OK;
@@ -973,8 +955,7 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
     CU_TRY(h, cudaSetDevice(c.device));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int T = n_tokens, H = c.hidden_dim, E = c.n_experts, K = c.experts_per_token;
-    int rb, route_cs;
-    route_shape(T, ceil_div(E, 32), h->n_sms, &rb, &route_cs);
+    const int rb = route_block_tokens(T, ceil_div(E, 32));
     const int nblk = ceil_div(T, rb);
     const int bn_local = pick_bn(h, T * K);  // ep_size == 1: the GEMMs run on this rank's own rows
     // Programmatic dependent launch pays for small batches (decode20b: 4.20 -> 4.05 ms per
@@ -1000,8 +981,8 @@ moe_b200_status forward_impl(moe_b200_handle h, int layer, const void* t, int t_
             t_dtype = MOE_B200_DTYPE_BF16;
         }
         RouteArgs ra{t, 0, T, H, lw.w_router, lw.b_router, E, K, router_score_out, h->topk_i, h->topk_w,
-                     h->blk_hist, pdl};
-        CU_TRY(h, launch_route(c.device, ra, rb, route_cs, s));
+                     h->blk_hist, pdl, h->n_sms};
+        CU_TRY(h, launch_route(c.device, ra, rb, s));
         prof_mark(h, MOE_B200_STAGE_ROUTE, false, s);
         h->last_launches++;
     }
@@ -1551,8 +1532,8 @@ moe_b200_status moe_b200_route_noalloc(const void* t, int t_dtype, int n_tokens,
     const int nblk = ceil_div(n_tokens, rb);
     RouteArgs ra{t, t_dtype == MOE_B200_DTYPE_F32, n_tokens, hidden_dim,
                  static_cast<const uint16_t*>(w_router_bf16), b_router, n_experts, experts_per_token,
-                 nullptr, topk_i_out, topk_w_out, blk_hist, false};
-    CU_TRY(nullptr, launch_route(dev, ra, rb, 1, st));
+                 nullptr, topk_i_out, topk_w_out, blk_hist, false, 0};
+    CU_TRY(nullptr, launch_route(dev, ra, rb, st));
     plan_kernel<<<1, 256, 0, st>>>(blk_hist, nblk, n_experts, 1, expert_counts_out, expert_offsets_out,
                                    tile_start, blk_base);
     CU_TRY(nullptr, cudaGetLastError());

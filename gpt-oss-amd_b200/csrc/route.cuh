@@ -251,18 +251,18 @@ __device__ __forceinline__ uint32_t route_cluster_rank() {
 __device__ __forceinline__ void route_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// The float at the same shared-memory address in CTA `rank` of the cluster.  Volatile (it
+// The four floats at the same shared-memory address in CTA `rank` of the cluster.  Volatile (it
 // stays behind the cluster barrier, itself a volatile asm) but without a memory clobber:
 // the loads of one element from all ranks are independent and overlap -- a remote
 // shared-memory load takes several hundred cycles.
-__device__ __forceinline__ float route_ld_remote(const float* p, uint32_t rank) {
-    float v;
+__device__ __forceinline__ float4 route_ld_remote(const float4* p, uint32_t rank) {
+    float4 v;
     const uint32_t la = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile(
         "{\n\t.reg .b32 ra;\n\t"
-        "mapa.shared::cluster.u32 ra, %1, %2;\n\t"
-        "ld.shared::cluster.f32 %0, [ra];\n\t}"
-        : "=f"(v) : "r"(la), "r"(rank));
+        "mapa.shared::cluster.u32 ra, %4, %5;\n\t"
+        "ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [ra];\n\t}"
+        : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(la), "r"(rank));
     return v;
 }
 
@@ -460,25 +460,40 @@ route_tc_kernel(const void* __restrict__ xv, int T, int H, const uint16_t* __res
     if (CS > 1) {
         route_cluster_sync();  // every CTA's partial sums are in its shared memory
         if (crank == 0) {
-            constexpr int PER = RBT * EP / RTHREADS;  // elements per thread: 2 NT MT
-            constexpr int BATCH = PER < 4 ? PER : 4;  // elements whose remote loads are in flight together
-            for (int j0 = 0; j0 < PER; j0 += BATCH) {
-                float part[BATCH][CS];
+            constexpr int N4 = RBT * EP / 4;  // float4 elements of the logits tile
+            float4* lg4 = reinterpret_cast<float4*>(lg);
+            for (int i0 = tid; i0 < N4; i0 += 2 * RTHREADS) {
+                // two elements per round: their remote loads are in flight together
+                float4 part[2][CS];
 #pragma unroll
-                for (int j = 0; j < BATCH; j++) {
-                    part[j][0] = lg[tid + (j0 + j) * RTHREADS];
+                for (int j = 0; j < 2; j++) {
+                    const int i = i0 + j * RTHREADS;
+                    if (i < N4) {
+                        part[j][0] = lg4[i];
 #pragma unroll
-                    for (int r = 1; r < CS; r++)
-                        part[j][r] = route_ld_remote(lg + tid + (j0 + j) * RTHREADS, (uint32_t)r);
+                        for (int r = 1; r < CS; r++)
+                            part[j][r] = route_ld_remote(lg4 + i, (uint32_t)r);
+                    }
                 }
 #pragma unroll
-                for (int j = 0; j < BATCH; j++) {
-                    float v = part[j][0];
+                for (int j = 0; j < 2; j++) {
+                    const int i = i0 + j * RTHREADS;
+                    if (i < N4) {
+                        float4 v = part[j][0];
 #pragma unroll
-                    for (int r = 1; r < CS; r++)
-                        v += part[j][r];  // rank order: the sum does not depend on timing
-                    const int e = (tid + (j0 + j) * RTHREADS) % EP;
-                    lg[tid + (j0 + j) * RTHREADS] = (e < E) ? v + b_router[e] : -INFINITY;
+                        for (int r = 1; r < CS; r++) {  // rank order: the sum does not depend on timing
+                            v.x += part[j][r].x;
+                            v.y += part[j][r].y;
+                            v.z += part[j][r].z;
+                            v.w += part[j][r].w;
+                        }
+                        const int e = (4 * i) % EP;  // EP is a multiple of 4: the four share a token row
+                        v.x = (e + 0 < E) ? v.x + b_router[e + 0] : -INFINITY;
+                        v.y = (e + 1 < E) ? v.y + b_router[e + 1] : -INFINITY;
+                        v.z = (e + 2 < E) ? v.z + b_router[e + 2] : -INFINITY;
+                        v.w = (e + 3 < E) ? v.w + b_router[e + 3] : -INFINITY;
+                        lg4[i] = v;
+                    }
                 }
             }
         }
