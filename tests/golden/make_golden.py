@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory by RUNNING THE REFERENCE.
 
-Needs the reference checkout (default /root/reference, override with
-MOE_REFERENCE_ROOT) and ``make -C oracle ref``; the fixtures it writes are
+Needs the reference checkout (its location: the MOE_REFERENCE_ROOT environment
+variable, else the default below) and ``make -C oracle ref``; the fixtures it writes are
 committed so the tests need neither.
 
 * ``mxfp4_table.npz``   -- every (e2m1 code, e8m0 scale byte) pair decoded by the
