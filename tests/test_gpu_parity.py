@@ -491,3 +491,17 @@ def test_unaligned_pointers_are_refused():
             eng.forward(0, good, out=out_flat[1:1 + 8 * 128].view(8, 128))
         torch.cuda.synchronize()
         assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("T", [40, 300, 1000, 3000])
+def test_block_is_bit_reproducible(T):
+    """Same inputs, same bits: the router's K split over a cluster adds its partial sums in
+    rank order, placement is stable, the combine adds in ascending expert order -- nothing
+    depends on timing.  The batch sizes cover clusters of 8, 4 and 2 CTAs and none."""
+    shape = pkg.MoEShape(hidden=320, intermediate=128, n_experts=40, top_k=4)
+    lw = synth.make_layer(shape, seed=17)
+    x_bits = synth.make_tokens(T, shape.hidden, seed=T)
+    a = run_gpu(shape, lw, x_bits, capi.GEMM_TCGEN05)
+    b = run_gpu(shape, lw, x_bits, capi.GEMM_TCGEN05)
+    for key in ("out", "score", "topk_i", "topk_w", "h_bits"):
+        assert np.array_equal(a[key], b[key]), key
