@@ -17,21 +17,35 @@
 
 namespace moe {
 
-// One block.  blk_hist [nblk, E] -> cnt[E], off[E+1] (rows sorted by expert),
-// blk_base[nblk, E] (first row of block b's assignments to expert e), and the
+// One block of 256 threads.  blk_hist [nblk, E] -> cnt[E], off[E+1] (rows sorted by
+// expert), blk_base[nblk, E] (first row of block b's assignments to expert e), and the
 // GEMM tile table tile_start[E+1] = prefix of ceil(cnt/bn).  s_cnt[256] (shared)
 // holds the counts for every thread when the function returns.
+// A thread walks one expert's column of the histogram (coalesced across the threads
+// of a warp); with fewer than 129 experts the 256 threads split the routing blocks
+// into 256 / E parts, which shortens the chain of dependent steps accordingly.
 __device__ __forceinline__ void plan_body(const int* __restrict__ blk_hist, int nblk, int E, int bn,
                                           int* __restrict__ cnt, int* __restrict__ off,
                                           int* __restrict__ tile_start, int* __restrict__ blk_base,
                                           int* s_cnt) {
     __shared__ int s_off[257];
-    const int e = threadIdx.x;
-    int total = 0;
-    if (e < E) {
-        for (int b = 0; b < nblk; b++)
-            total += blk_hist[(size_t)b * E + e];
-        s_cnt[e] = total;
+    __shared__ int s_part[256];
+    const int P = max(1, 256 / E);  // parts of the block range
+    const int part = (int)threadIdx.x / E, e = (int)threadIdx.x - part * E;
+    const bool active = part < P;
+    const int b_lo = active ? (int)((long long)nblk * part / P) : 0;
+    const int b_hi = active ? (int)((long long)nblk * (part + 1) / P) : 0;
+    int sum = 0;
+    for (int b = b_lo; b < b_hi; b++)
+        sum += blk_hist[(size_t)b * E + e];
+    if (active)
+        s_part[threadIdx.x] = sum;
+    __syncthreads();
+    if ((int)threadIdx.x < E) {
+        int total = 0;
+        for (int p = 0; p < P; p++)
+            total += s_part[p * E + threadIdx.x];
+        s_cnt[threadIdx.x] = total;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -49,9 +63,11 @@ __device__ __forceinline__ void plan_body(const int* __restrict__ blk_hist, int 
         tile_start[E] = t;
     }
     __syncthreads();
-    if (e < E) {
+    if (active) {
         int run = s_off[e];
-        for (int b = 0; b < nblk; b++) {
+        for (int p = 0; p < part; p++)
+            run += s_part[p * E + e];
+        for (int b = b_lo; b < b_hi; b++) {
             blk_base[(size_t)b * E + e] = run;
             run += blk_hist[(size_t)b * E + e];
         }
@@ -161,8 +177,11 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
         s_e[a] = e;
     }
     __syncthreads();
-    const int per = (n_assign + gridDim.y - 1) / gridDim.y;
-    const int a_lo = blockIdx.y * per, a_hi = min(n_assign, a_lo + per);
+    // the gridDim.y blocks of a routing block split its TOKENS (all K assignments of a
+    // token stay together: its row is read once and stored K times)
+    const int tok_per = (rb + gridDim.y - 1) / gridDim.y;
+    const int tl_lo = blockIdx.y * tok_per, tl_hi = min(rb, tl_lo + tok_per);
+    const int a_lo = tl_lo * K, a_hi = tl_hi * K;
     for (int a = a_lo + threadIdx.x; a < a_hi; a += blockDim.x) {
         const int e = s_e[a];
         int pos = -1;
@@ -179,23 +198,42 @@ permute_kernel(const void* __restrict__ x, int x_is_f32, int T, int H, int K, in
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int vec_per_row = H / 8;  // 8 bf16 = 16 bytes
-    for (int a = a_lo + warp; a < a_hi; a += nwarps) {
-        const int pos = s_pos[a];
-        if (pos < 0)
-            continue;
-        const int t = t0 + a / K;
-        uint4* dst = reinterpret_cast<uint4*>(xs_out + (size_t)pos * H);
+    // a warp takes a quarter of a token's row at a time: a block that holds only a few
+    // tokens still keeps all its warps busy
+    constexpr int NSEG = 4;
+    const int seg_len = (vec_per_row + NSEG - 1) / NSEG;
+    for (int item = tl_lo * NSEG + warp; item < tl_hi * NSEG; item += nwarps) {
+        const int tl = item / NSEG, seg = item - tl * NSEG;
+        const int t = t0 + tl;
+        if (t >= T)
+            break;
+        const int v_lo = seg * seg_len, v_hi = min(vec_per_row, v_lo + seg_len);
+        uint4* dst[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int pos = k < K ? s_pos[tl * K + k] : -1;
+            dst[k] = pos >= 0 ? reinterpret_cast<uint4*>(xs_out + (size_t)pos * H) : nullptr;
+        }
         if (x_is_f32) {
             const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)t * H);
-            for (int v = lane; v < vec_per_row; v += 32) {
-                float4 p = src[2 * v], q = src[2 * v + 1];
-                dst[v] = make_uint4(pack_bf16x2(p.x, p.y), pack_bf16x2(p.z, p.w),
-                                    pack_bf16x2(q.x, q.y), pack_bf16x2(q.z, q.w));
+            for (int v = v_lo + lane; v < v_hi; v += 32) {
+                const float4 p = src[2 * v], q = src[2 * v + 1];
+                const uint4 r = make_uint4(pack_bf16x2(p.x, p.y), pack_bf16x2(p.z, p.w),
+                                           pack_bf16x2(q.x, q.y), pack_bf16x2(q.z, q.w));
+#pragma unroll
+                for (int k = 0; k < 8; k++)
+                    if (dst[k])
+                        dst[k][v] = r;
             }
         } else {
             const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + (size_t)t * H);
-            for (int v = lane; v < vec_per_row; v += 32)
-                dst[v] = src[v];
+            for (int v = v_lo + lane; v < v_hi; v += 32) {
+                const uint4 r = src[v];
+#pragma unroll
+                for (int k = 0; k < 8; k++)
+                    if (dst[k])
+                        dst[k][v] = r;
+            }
         }
     }
 }

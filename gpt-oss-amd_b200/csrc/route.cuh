@@ -48,7 +48,8 @@ constexpr int RTHREADS = 256;
 // SM, each a chain of H / 64 dependent chunks whose length in time is the number of
 // load round trips) take as many as fit in ~200 KB of shared memory, at most 28; the 64-token blocks
 // of large batches stay under half of it so that two blocks share an SM and a batch of
-// 16384 tokens (256 blocks) runs as one wave.
+// 16384 tokens (256 blocks) runs as one wave (measured: 0.113 ms so, 0.172 ms with a
+// 7-stage ring and one block per SM in two waves).
 // A CTA of a K-splitting cluster (CS > 1) walks only 1/CS of the chunks: 8 stages cover them.
 template <int NT, int MT, int CS = 1>
 __host__ __device__ constexpr int route_tc_stages() {
