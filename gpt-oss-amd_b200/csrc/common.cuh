@@ -21,11 +21,12 @@ namespace moe {
 //   [4096 , 4352)  scales : row r's two e8m0 bytes at r*2
 //
 // Inside a 16-byte block the four 32-bit words each cover 8 consecutive
-// columns; the eight e2m1 codes of a word are stored with the even columns in
-// nibbles 0..3 and the odd columns in nibbles 4..7, so columns (2p, 2p+1) sit 16
-// bits apart and one shift places both into a bf16x2 register.  Every nibble
-// is still an e2m1 code and every scale an e8m0 byte: only their order differs
-// from the checkpoint layout.  Rows past the end of the matrix are zero codes.
+// columns; the 32 bits of a word are the 32 bits of its eight e2m1 codes, moved
+// to the positions from which mxfp4_decode_word (below) needs the fewest shifts
+// and masks: even columns in the low half, odd columns in the high half, so
+// columns (2p, 2p+1) sit 16 bits apart and land in one bf16x2 register.  Every
+// bit is still a bit of an e2m1 code and every scale an e8m0 byte: 4.25 bits per
+// weight, as in the checkpoint.  Rows past the end of the matrix are zero codes.
 constexpr int TILE_M = 128;
 constexpr int KSTAGE = 64;
 constexpr int PLANE_BYTES = TILE_M * 16;
@@ -90,30 +91,49 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// Eight columns: word w (resident nibble order) -> out[p] = bf16x2 of columns
-// (2p, 2p+1), low half = even column.
+// Resident word: the eight e2m1 codes of eight consecutive columns, bit-scattered so
+// that the decode needs as few shifts and masks as the bf16 layout allows.  Even columns
+// live in the low 16-bit half, odd columns in the high half, at the same positions; the
+// codes of columns (2p, 2p+1) make output p.  A code s|e1 e0|m must end up with
+// e1 e0 m at bits [8:6] and s at bit 15 of its half, i.e. on the bit pattern
+// {a, a+1, a+2, a+9} shifted left by 6 - a.  That pattern fits a 16-bit half three
+// times (a = 6, 3, 0: bits 0..9, 12, 15); the fourth code takes the four bits left
+// over (10, 11, 13, 14) and pays for it with three shifts:
+//   half bit   15  14  13  12  11  10   9  8..6  5..3  2..0
+//   holds      s0  s3  e1  s1  e0   m  s2   c0    c1    c2       (c = e1 e0 m; e1, e0, m, s3 of code 3)
+// Per word: 5 shifts, 6 logic operations, 4 bf16x2 multiplies (a nibble-per-code word
+// needs 7 + 8 + 4).
 __device__ __forceinline__ void mxfp4_decode_word(uint32_t w, uint32_t mult, uint32_t out[4]) {
-    const uint32_t MAG = 0x01C001C0u, SGN = 0x80008000u;
-    uint32_t b0 = ((w << 6) & MAG) | ((w << 12) & SGN);
-    uint32_t b1 = ((w << 2) & MAG) | ((w << 8) & SGN);
-    uint32_t b2 = ((w >> 2) & MAG) | ((w << 4) & SGN);
-    uint32_t b3 = ((w >> 6) & MAG) | (w & SGN);
+    const uint32_t CODE = 0x81C081C0u;  // sign and magnitude of a code in place, both halves
+    const uint32_t b0 = w & CODE;
+    const uint32_t b1 = (w << 3) & CODE;
+    const uint32_t b2 = (w << 6) & CODE;
+    // code 3: (e0, m) from bits 11:10, e1 from bit 13, the sign from bit 14
+    const uint32_t em = w >> 4, e1 = w >> 5, sg = w << 1;
+    const uint32_t mag = (em & 0x00C000C0u) | (e1 & ~0x00C000C0u);  // one bit-select
+    const uint32_t b3 = ((sg & 0x80008000u) | (mag & ~0x80008000u)) & CODE;
     out[0] = bf16x2_mul(b0, mult);
     out[1] = bf16x2_mul(b1, mult);
     out[2] = bf16x2_mul(b2, mult);
     out[3] = bf16x2_mul(b3, mult);
 }
 
-// Checkpoint word (nibble i = column i) -> resident word (even columns in the
-// low half, odd columns in the high half).
+// Checkpoint word (nibble i = column i, bit 3 of a nibble = sign) -> resident word.
 __host__ __device__ __forceinline__ uint32_t mxfp4_retile_word(uint32_t w) {
-    uint32_t even = w & 0x0F0F0F0Fu;
-    uint32_t odd = (w >> 4) & 0x0F0F0F0Fu;
-    uint32_t lo = (even & 0xFu) | ((even >> 4) & 0xF0u) | ((even >> 8) & 0xF00u) |
-                  ((even >> 12) & 0xF000u);
-    uint32_t hi = (odd & 0xFu) | ((odd >> 4) & 0xF0u) | ((odd >> 8) & 0xF00u) |
-                  ((odd >> 12) & 0xF000u);
-    return lo | (hi << 16);
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t c = (w >> (4 * i)) & 0xFu, mag = c & 7u, sgn = c >> 3;
+        uint32_t h;
+        switch (i >> 1) {
+            case 0: h = (mag << 6) | (sgn << 15); break;
+            case 1: h = (mag << 3) | (sgn << 12); break;
+            case 2: h = mag | (sgn << 9); break;
+            default: h = ((mag & 3u) << 10) | ((mag >> 2) << 13) | (sgn << 14); break;
+        }
+        r |= h << (16 * (i & 1));
+    }
+    return r;
 }
 
 // Exact decode of one element for ANY scale byte, integer arithmetic only:
