@@ -93,45 +93,53 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
 
 // Resident word: the eight e2m1 codes of eight consecutive columns, bit-scattered so
 // that the decode needs as few shifts and masks as the bf16 layout allows.  Even columns
-// live in the low 16-bit half, odd columns in the high half, at the same positions; the
-// codes of columns (2p, 2p+1) make output p.  A code s|e1 e0|m must end up with
-// e1 e0 m at bits [8:6] and s at bit 15 of its half, i.e. on the bit pattern
-// {a, a+1, a+2, a+9} shifted left by 6 - a.  That pattern fits a 16-bit half three
-// times (a = 6, 3, 0: bits 0..9, 12, 15); the fourth code takes the four bits left
-// over (10, 11, 13, 14) and pays for it with three shifts:
-//   half bit   15  14  13  12  11  10   9  8..6  5..3  2..0
-//   holds      s0  s3  e1  s1  e0   m  s2   c0    c1    c2       (c = e1 e0 m; e1, e0, m, s3 of code 3)
-// Per word: 5 shifts, 6 logic operations, 4 bf16x2 multiplies (a nibble-per-code word
-// needs 7 + 8 + 4).
+// belong to the low 16-bit half of an output, odd columns to the high half; the codes of
+// columns (2p, 2p+1) make output p.  A code s|e1 e0|m must end up with e1 e0 m at
+// bits [8:6] and s at bit 15 of its half, so a code that one rotation of the word by r
+// puts in place sits on the bits {a, a+1, a+2, a+9} (+16 for the other half, mod 32)
+// with a = 6 - r.  Modulo 16 that pattern fits three times but never four (enumerated);
+// of all layouts the one below decodes in the fewest operations: three codes on the
+// pattern (a = 0, 4, 10), the fourth with e1, e0, s already in place and only its m
+// one rotation away.
+//   output 0: m e0 e1 s at bits  0  1  2  9 | 16 17 18 25   (low-half code | high-half code)
+//   output 1:                    4  5  6 13 | 20 21 22 29
+//   output 2:                   10 11 12 19 | 26 27 28  3
+//   output 3:                   30  7  8 15 | 14 23 24 31
+// Per word: 4 shifts or rotations, 5 logic operations, 4 bf16x2 multiplies (a
+// nibble-per-code word needs 7 + 8 + 4).
+// Bit of the resident word that holds bit `b` (0 = m, 1 = e0, 2 = e1, 3 = s) of the code
+// of output `o`, half `h`: the table above, five bits per entry.
+__host__ __device__ constexpr int mxfp4_resident_pos(int o, int h, int b) {
+    constexpr unsigned long long LO[4] = {  // four positions per (output, low half), 8 bits each
+        0x09020100ull, 0x0D060504ull, 0x130C0B0Aull, 0x0F08071Eull};
+    constexpr unsigned long long HI[4] = {
+        0x19121110ull, 0x1D161514ull, 0x031C1B1Aull, 0x1F18170Eull};
+    return (int)(((h ? HI[o] : LO[o]) >> (8 * b)) & 0xFFull);
+}
+
 __device__ __forceinline__ void mxfp4_decode_word(uint32_t w, uint32_t mult, uint32_t out[4]) {
     const uint32_t CODE = 0x81C081C0u;  // sign and magnitude of a code in place, both halves
-    const uint32_t b0 = w & CODE;
-    const uint32_t b1 = (w << 3) & CODE;
-    const uint32_t b2 = (w << 6) & CODE;
-    // code 3: (e0, m) from bits 11:10, e1 from bit 13, the sign from bit 14
-    const uint32_t em = w >> 4, e1 = w >> 5, sg = w << 1;
-    const uint32_t mag = (em & 0x00C000C0u) | (e1 & ~0x00C000C0u);  // one bit-select
-    const uint32_t b3 = ((sg & 0x80008000u) | (mag & ~0x80008000u)) & CODE;
+    const uint32_t M_BIT = 0x00400040u;
+    const uint32_t b0 = (w << 6) & CODE;
+    const uint32_t b1 = (w << 2) & CODE;
+    const uint32_t b2 = __funnelshift_r(w, w, 4) & CODE;
+    const uint32_t r8 = __funnelshift_l(w, w, 8);
+    const uint32_t b3 = ((r8 & M_BIT) | (w & ~M_BIT)) & CODE;  // a bit-select, then the mask
     out[0] = bf16x2_mul(b0, mult);
     out[1] = bf16x2_mul(b1, mult);
     out[2] = bf16x2_mul(b2, mult);
     out[3] = bf16x2_mul(b3, mult);
 }
 
-// Checkpoint word (nibble i = column i, bit 3 of a nibble = sign) -> resident word.
+// Checkpoint word (nibble i = column i; bits of a nibble: m, e0, e1, s) -> resident word.
 __host__ __device__ __forceinline__ uint32_t mxfp4_retile_word(uint32_t w) {
     uint32_t r = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const uint32_t c = (w >> (4 * i)) & 0xFu, mag = c & 7u, sgn = c >> 3;
-        uint32_t h;
-        switch (i >> 1) {
-            case 0: h = (mag << 6) | (sgn << 15); break;
-            case 1: h = (mag << 3) | (sgn << 12); break;
-            case 2: h = mag | (sgn << 9); break;
-            default: h = ((mag & 3u) << 10) | ((mag >> 2) << 13) | (sgn << 14); break;
-        }
-        r |= h << (16 * (i & 1));
+        const uint32_t c = (w >> (4 * i)) & 0xFu;
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+            r |= ((c >> b) & 1u) << mxfp4_resident_pos(i >> 1, i & 1, b);
     }
     return r;
 }
