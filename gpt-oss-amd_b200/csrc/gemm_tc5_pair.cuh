@@ -342,7 +342,7 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
             int it = 0;
             for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs, ++it) {
                 for (int ks = 0; ks < k_stages; ks++) {
-                    ok = mbar_wait(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
+                    ok = mbar_wait_hot(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok)
                         break;
@@ -371,7 +371,7 @@ expert_gemm_pair_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* 
                 const uint32_t idesc = make_idesc2(ti.n_mma);
                 for (int ks = 0; ks < k_stages; ks++) {
                     if (!ready) {
-                        ok = mbar_wait(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
+                        ok = mbar_wait_hot(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok)
                             break;

@@ -355,7 +355,7 @@ expert_gemm_ts_kernel(const __grid_constant__ TensorMaps maps, const uint8_t* __
             const int need = ti.n_mma >> 5;                    // B units per step
             const uint32_t sub_step = (uint32_t)ti.n_mma * 8u;  // one chunk's tile in descriptor units of 16 bytes
             for (int st = 0; st < n_steps; st++) {
-                ok = mbar_wait(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
+                ok = mbar_wait_hot(bar_full(nb), ph, status, DS_TIMEOUT_FULL_A, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok)
                     break;
