@@ -44,18 +44,18 @@ constexpr int RMK = 64;          // K chunk: terms the tensor core sums before a
 constexpr int RMLD = RMK + 8;    // bf16 per smem row: conflict-free fragment loads
 constexpr int RTHREADS = 256;
 
-// Stages of the cp.async ring.  Short blocks (small batches: at most a block or two per
-// SM, each a chain of H / 64 dependent chunks whose length in time is the number of
-// load round trips) take as many as fit in ~200 KB of shared memory, at most 28 (12 for 32-token
-// blocks, so that two of them with few experts still share an SM); the 64-token blocks
-// of large batches stay under half of it so that two blocks share an SM and a batch of
-// 16384 tokens (256 blocks) runs as one wave (measured: 0.113 ms so, 0.172 ms with a
-// 7-stage ring and one block per SM in two waves).
+// Stages of the cp.async ring.  16-token blocks (small batches: at most a block per SM,
+// each a chain of H / 64 dependent chunks whose length in time is the number of load
+// round trips) take as many as fit in ~200 KB of shared memory, at most 28.  The 32- and
+// 64-token blocks of larger batches stay under half of it so that two blocks share an SM
+// and 8192 or 16384 tokens (256 blocks) run as one wave.  Measured, E = 128: 8192 tokens
+// 0.080 ms with 8 stages and one block per SM, 0.060 with 4 stages and two; 16384 tokens
+// 0.113 ms with 3 stages and two blocks per SM, 0.172 with 7 stages and one.
 // A CTA of a K-splitting cluster (CS > 1) walks only 1/CS of the chunks: 8 stages cover them.
 template <int NT, int MT, int CS = 1>
 __host__ __device__ constexpr int route_tc_stages() {
     constexpr int stage_bytes = (16 * MT + 32 * NT) * RMLD * 2;
-    constexpr int budget = (MT == 4 && CS == 1 ? 100 : 200) * 1024;
+    constexpr int budget = (MT >= 2 && CS == 1 ? 100 : 200) * 1024;
     constexpr int fit = budget / stage_bytes;
     constexpr int cap = CS > 1 ? 8 : (MT == 1 ? 28 : 12);
     return fit > cap ? cap : (fit < 3 ? 3 : fit);
