@@ -155,6 +155,7 @@ CASES = [
     (320, 192, 4, 2, 700),    # large-batch GEMM kernel with partial weight tiles
     (128, 64, 128, 4, 4000),  # large-batch (CTA-pair) GEMM kernel with 128 experts, 125 rows each
     (192, 128, 128, 4, 9000), # the same above 256 rows per expert: several token tiles per expert
+    (128, 64, 64, 4, 9600),   # 64-token routing blocks (above 9472 tokens)
 ]
 
 
